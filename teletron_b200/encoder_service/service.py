@@ -1,0 +1,234 @@
+"""Distributed multimodal-encoder service: producer ranks and their DiT-side consumers.
+
+Dedicated ranks at the tail of the world run the VAE and the two text encoders and stream one
+flat message per sample to the first rank of each TP x CP block over ``torch.distributed`` p2p
+(NCCL on GPU), as in ``teletron/models/hunyuanvideo/producer.py:105-236`` and
+``teletron/training/utils.py:84-174``.  What differs:
+
+* the consumer keeps one ``irecv`` posted *ahead* of the step that needs it, so the transfer runs
+  under DiT compute instead of blocking at the top of the step (``utils.py:115-116``);
+* the receive buffer is sized from the flags (the reference pulls a full sample from a local
+  dataloader just to read its shape, ``utils.py:98-110``);
+* messages carry a checked header (:mod:`.protocol`), waits are bounded and raise
+  :class:`EncoderTimeout`, and a consumer that loses its producer can fall back to a local sample
+  source instead of hanging until the process-group timeout;
+* producers use their own device (``LOCAL_RANK``), not ``cuda:{rank - dit_world}`` which aliases
+  DiT GPUs on one node (``producer.py:113-115``).
+"""
+
+from __future__ import annotations
+
+import collections
+import time
+from typing import Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..parallel import state as ps
+from ..parallel.state import CommPair
+from .protocol import MessageSpec, ProtocolError, pack_message, unpack_message
+
+QUEUE_DEPTH = 2            # encoded samples buffered per consumer (producer.py:24-26)
+MAX_OUTSTANDING_SENDS = 1
+
+
+class EncoderTimeout(RuntimeError):
+    pass
+
+
+def _wait(req, timeout: Optional[float], what: str):
+    """Bounded wait on a p2p request: polls ``is_completed`` so a lost peer surfaces as an exception."""
+    if timeout is None or timeout <= 0:
+        req.wait()
+        return
+    t0 = time.monotonic()
+    while not req.is_completed():
+        if time.monotonic() - t0 > timeout:
+            raise EncoderTimeout(f"timed out after {timeout:.1f}s waiting for {what}")
+        time.sleep(0.001)
+    req.wait()
+
+
+class Encoders:
+    """The three encoders a producer runs.  Each is a callable so tests can plug in stand-ins.
+
+    ``vae(pixels [B, 3, F, H, W]) -> latents [B, 16, f, h, w]`` (already scaled),
+    ``text(prompts: List[str]) -> (embeds [B, L, 4096], mask [B, L])``, ``clip(prompts) -> [B, 768]``.
+    """
+
+    def __init__(self, vae: Callable, text: Callable, clip: Callable):
+        self.vae, self.text, self.clip = vae, text, clip
+
+    @staticmethod
+    def build_default(device, dtype=torch.bfloat16, vae_tiling: bool = True, max_text_len: int = 256) -> "Encoders":
+        from ..models.vae import AutoencoderKLHunyuanVideo
+        from ..models.text_encoders import ClipTextEncoder, LlamaTextEncoder
+        vae = AutoencoderKLHunyuanVideo().to(device, dtype).eval()
+        vae.enable_tiling(vae_tiling)
+        llama = LlamaTextEncoder(max_length=max_text_len, device=device, dtype=dtype)
+        clip = ClipTextEncoder(device=device, dtype=dtype)
+        sf = 0.476986
+
+        @torch.no_grad()
+        def vae_fn(pixels):
+            return vae.encode(pixels.to(device, dtype)) * sf
+        return Encoders(vae_fn, llama, clip)
+
+
+def encode_sample(sample: Dict, enc: Encoders, spec: MessageSpec, seq: int, device) -> torch.Tensor:
+    """Dataset item (or collated batch of 1) -> packed message on ``device``."""
+    images = sample["images"]
+    if images.dim() == 4:
+        images = images[None]
+    pixels = images.permute(0, 2, 1, 3, 4)                                  # [B, 3, F, H, W]
+    latents = enc.vae(pixels)
+    first = sample.get("first_ref_image")
+    if first is None:
+        first_px = pixels[:, :, :1]
+    else:
+        first = first if first.dim() == 4 else first[None]                   # [B, 3, H, W]
+        first_px = first[:, :, None]
+    first_lat = enc.vae(first_px)
+    prompt = sample["prompt"]
+    prompts = list(prompt) if isinstance(prompt, (list, tuple)) else [prompt]
+    embeds, mask = enc.text(prompts)
+    L = int(mask[0].sum())
+    pooled = enc.clip(prompts)
+    return pack_message(spec, seq, embeds[0, :L].to(device, torch.bfloat16), pooled[0].to(device, torch.bfloat16),
+                        first_lat[0].to(device, torch.bfloat16), latents[0].to(device, torch.bfloat16))
+
+
+def producer_loop(pairs: List[CommPair], iterators: Dict[int, object], encode: Callable[[Dict, int], torch.Tensor],
+                  start_seq: Dict[int, int], max_items: Optional[int] = None, idle_sleep: float = 0.002,
+                  drop: Optional[Callable[[int, int], bool]] = None) -> Dict[int, int]:
+    """Round-robin service of all consumers: keep up to ``QUEUE_DEPTH`` encoded samples per consumer and
+    one outstanding ``isend`` each.  ``drop(consumer, seq)`` is a host-side fault-injection hook for the
+    tests (a message that is encoded but never sent).  Returns the number of messages sent per consumer."""
+    queues = {p.consumer: collections.deque() for p in pairs}
+    inflight = {p.consumer: collections.deque() for p in pairs}
+    seq = dict(start_seq)
+    sent = {p.consumer: 0 for p in pairs}
+    produced = {p.consumer: 0 for p in pairs}
+    exhausted = set()
+    while True:
+        progress = False
+        for p in pairs:
+            c = p.consumer
+            while inflight[c] and inflight[c][0][0].is_completed():
+                inflight[c].popleft()
+                progress = True
+            if c not in exhausted and len(queues[c]) < QUEUE_DEPTH and (max_items is None or produced[c] < max_items):
+                try:
+                    sample = next(iterators[c])
+                except StopIteration:
+                    exhausted.add(c)
+                    continue
+                queues[c].append((seq[c], encode(sample, seq[c])))
+                seq[c] += 1
+                produced[c] += 1
+                progress = True
+            if queues[c] and len(inflight[c]) < MAX_OUTSTANDING_SENDS:
+                s, msg = queues[c].popleft()
+                if drop is not None and drop(c, s):
+                    continue
+                inflight[c].append((dist.isend(msg, dst=c), msg))
+                sent[c] += 1
+                progress = True
+        done = all((c in exhausted or (max_items is not None and produced[c] >= max_items))
+                   and not queues[c] and not inflight[c] for c in queues)
+        if done:
+            return sent
+        if not progress:
+            time.sleep(idle_sleep)
+
+
+def producer_process(args, train_valid_test_datasets_provider: Callable, encoders: Optional[Encoders] = None) -> None:
+    """Body of an encoder rank (called from :func:`teletron_b200.training.pretrain`)."""
+    from ..training.pretrain import build_train_valid_test_data_iterators
+    device = args.device
+    pairs = ps.get_producer_pairs()
+    if not pairs:
+        return
+    spec = MessageSpec.from_flags(args.num_frames, args.video_resolution)
+    enc = encoders or Encoders.build_default(device, args.params_dtype, vae_tiling=bool(args.vae_tiling))
+    # handshake: every consumer tells us the iteration it resumes from (training.py:208-220, producer.py:137-153)
+    start = {}
+    reqs = []
+    for p in pairs:
+        t = torch.zeros(1, dtype=torch.int64, device=device)
+        reqs.append((p, t, dist.irecv(t, src=p.consumer)))
+    for p, t, r in reqs:
+        _wait(r, args.distributed_timeout_minutes * 60.0, f"handshake from consumer {p.consumer}")
+        start[p.consumer] = int(t.item())
+    iterators = {}
+    for p in pairs:
+        args.consumed_train_samples = start[p.consumer] * args.global_batch_size
+        it, _, _ = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args,
+                                                         dp_rank=p.dp_rank, dp_size=p.dp_size)
+        iterators[p.consumer] = it
+    remaining = max(0, args.train_iters - min(start.values())) * args.num_microbatches
+    producer_loop(pairs, iterators, lambda s, q: encode_sample(s, enc, spec, q, device), start, max_items=remaining)
+
+
+class EncoderConsumer:
+    """DiT-side endpoint: double-buffered receive, one message always in flight ahead of use."""
+
+    def __init__(self, pair: CommPair, args=None, device=None, spec: Optional[MessageSpec] = None,
+                 timeout: Optional[float] = None, fallback: Optional[Callable[[], Dict]] = None):
+        self.pair = pair
+        self.device = device
+        self.spec = spec or MessageSpec.from_flags(args.num_frames, args.video_resolution)
+        self.timeout = timeout if timeout is not None else (args.distributed_timeout_minutes * 60.0 if args else None)
+        self.fallback = fallback
+        self._bufs = [torch.empty(self.spec.numel, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self._slot = 0
+        self._req = None
+        self._seq = 0
+        self._to_post = None        # receives still to post (None = unbounded)
+        self._args = args
+        self.bytes_received = 0
+
+    def handshake(self, iteration: int) -> None:
+        t = torch.tensor([iteration], dtype=torch.int64, device=self.device)
+        dist.isend(t, dst=self.pair.producer).wait()
+        self._seq = iteration
+        if self._args is not None:
+            # never leave an unmatched receive behind at shutdown
+            self._to_post = max(0, self._args.train_iters - iteration) * self._args.num_microbatches
+        self._post()
+
+    def _post(self):
+        if self._to_post is not None:
+            if self._to_post <= 0:
+                self._req = None
+                return
+            self._to_post -= 1
+        self._req = dist.irecv(self._bufs[self._slot], src=self.pair.producer)
+
+    def next_batch(self) -> Dict[str, torch.Tensor]:
+        """The sample for this step; immediately re-posts the receive for the next one."""
+        if self._req is None:
+            self._post()
+        if self._req is None:
+            raise RuntimeError("the encoder stream is exhausted (all scheduled samples were received)")
+        try:
+            _wait(self._req, self.timeout, f"sample {self._seq} from encoder rank {self.pair.producer}")
+            msg = self._bufs[self._slot]
+            out = unpack_message(self.spec, msg, expect_seq=self._seq)
+        except (EncoderTimeout, ProtocolError):
+            if self.fallback is None:
+                raise
+            self._req = None
+            self._seq += 1
+            return self.fallback()
+        self.bytes_received += self.spec.nbytes
+        self._seq += 1
+        self._slot ^= 1
+        self._post()                      # prefetch: lands while this step computes
+        out.pop("seq")
+        out.pop("text_len")
+        return out
+
+    def close(self):
+        self._req = None

@@ -1,0 +1,318 @@
+"""Dual-stream and single-stream MMDiT blocks with tensor + Ulysses context parallelism.
+
+Behaviour follows ``teletron/models/dit/dit_layerspec.py:81-186`` (dual block),
+``:248-358`` (single block), ``teletron/models/dit/dit_attention.py:43-338`` /
+``:340-504`` (joint / single attention) and ``teletron/models/dit/dit_fusedlayers.py:155-272``
+(AdaLN-zero modulation).  Parameter names match the reference's Megatron/TE modules so
+its converted checkpoints load: ``norm1.linear``, ``self_attention.linear_qkv``,
+``self_attention.added_linear_qkv``, ``self_attention.linear_proj``,
+``self_attention.{q,k,added_q,added_k}_layernorm.weight``, ``mlp.linear_fc1/2``,
+``ff_context.linear_fc1/2``, ``norm.linear``, ``proj_mlp``, ``proj_out``.
+
+The structure is not Megatron's: blocks are plain modules over the functional op layer
+(:mod:`teletron_b200.ops`), and the hot sequence is expressed with the fused ops that
+the sm_100a kernels implement (LayerNorm+modulate, QKV GEMM + QK-RMSNorm + RoPE,
+projection GEMM + gate + residual, GEMM + GELU).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import torch
+from torch import nn
+import torch.nn.functional as F
+
+from ... import ops
+from ...parallel import mappings as M
+from ...parallel import state as ps
+from ...parallel.pad import SeqPad
+
+
+# ---------------------------------------------------------------------------------------------
+# Tensor-parallel linears
+# ---------------------------------------------------------------------------------------------
+
+def _mark(param: nn.Parameter, *, partition_dim: Optional[int], full_shape: Sequence[int],
+          init: str, partitions: Optional[Sequence[int]] = None) -> None:
+    """Attach sharding / init metadata used by init, checkpointing and the converter."""
+    param.partition_dim = partition_dim          # None = replicated over tensor-parallel ranks
+    param.full_shape = tuple(full_shape)
+    param.init_kind = init                       # "normal" | "scaled_normal" | "zeros" | "ones"
+    param.partitions = tuple(partitions) if partitions else None
+    param.tensor_model_parallel = partition_dim is not None
+
+
+class ColumnParallelLinear(nn.Module):
+    """``y = act(x W^T + b)`` with ``W`` sharded over output features (rows)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, tp: int = 1,
+                 device=None, dtype=None):
+        super().__init__()
+        if out_features % tp:
+            raise ValueError(f"out_features {out_features} not divisible by tp {tp}")
+        self.in_features, self.out_features, self.tp = in_features, out_features, tp
+        self.weight = nn.Parameter(torch.empty(out_features // tp, in_features, device=device, dtype=dtype))
+        _mark(self.weight, partition_dim=0 if tp > 1 else None, full_shape=(out_features, in_features), init="normal")
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_features // tp, device=device, dtype=dtype))
+            _mark(self.bias, partition_dim=0 if tp > 1 else None, full_shape=(out_features,), init="zeros")
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor, activation: Optional[str] = None) -> torch.Tensor:
+        x = M.copy_to_tensor_model_parallel_region(x, ps.get_tensor_model_parallel_group())
+        return ops.linear(x, self.weight, self.bias, activation)
+
+
+class RowParallelLinear(nn.Module):
+    """``y = x W^T + b`` with ``W`` sharded over input features; output all-reduced over TP.
+
+    ``input_partitions`` describes an input made of several concatenated feature
+    groups that are *each* sharded (the single block's ``proj_out`` consumes
+    ``[attn 3072/tp | mlp 12288/tp]``, ``convert_hunyuanvideo.py:578-589``).
+    """
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, tp: int = 1,
+                 input_partitions: Optional[Sequence[int]] = None, device=None, dtype=None):
+        super().__init__()
+        if in_features % tp:
+            raise ValueError(f"in_features {in_features} not divisible by tp {tp}")
+        self.in_features, self.out_features, self.tp = in_features, out_features, tp
+        self.weight = nn.Parameter(torch.empty(out_features, in_features // tp, device=device, dtype=dtype))
+        _mark(self.weight, partition_dim=1 if tp > 1 else None, full_shape=(out_features, in_features),
+              init="scaled_normal", partitions=input_partitions)
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype))
+            _mark(self.bias, partition_dim=None, full_shape=(out_features,), init="zeros")
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Projection, TP all-reduce, bias (bias is added once, after the reduction)."""
+        if self.tp == 1:
+            return ops.linear(x, self.weight, self.bias)
+        y = ops.linear(x, self.weight, None)
+        y = M.reduce_from_tensor_model_parallel_region(y, ps.get_tensor_model_parallel_group())
+        return y if self.bias is None else y + self.bias
+
+    def forward_gate_residual(self, x: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """``residual + gate * (x W^T + b)``: one fused GEMM epilogue when ``tp == 1``."""
+        if self.tp == 1:
+            return ops.linear_gate_residual(x, self.weight, self.bias, gate, residual)
+        return ops.gate_residual(residual, self.forward(x), gate)
+
+
+class RMSNorm(nn.Module):
+    """Per-head RMSNorm.  ``tp_partial`` marks a weight that is shared by heads living on different
+    tensor-parallel ranks: each rank then sees only its heads' share of the gradient, and the shares
+    must be summed over TP before the optimizer step (the reference omits this reduction, so its
+    q/k norm weights drift apart between TP ranks)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6, tp_partial: bool = False, device=None, dtype=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+        _mark(self.weight, partition_dim=None, full_shape=(dim,), init="ones")
+        self.weight.tp_partial_grad = tp_partial
+
+    def forward(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps)
+
+
+class AdaLNModulation(nn.Module):
+    """``Linear(SiLU(temb))`` producing ``n_chunks`` modulation vectors.
+
+    Column-parallel over TP followed by an all-gather of the (tiny) output, as in
+    ``dit_fusedlayers.py:216-218``.  The LayerNorm itself is applied by the caller
+    through :func:`teletron_b200.ops.layernorm_modulate`.
+    """
+
+    def __init__(self, dim: int, n_chunks: int, tp: int = 1, device=None, dtype=None):
+        super().__init__()
+        self.n_chunks = n_chunks
+        self.linear = ColumnParallelLinear(dim, n_chunks * dim, bias=True, tp=tp, device=device, dtype=dtype)
+
+    def forward(self, temb: torch.Tensor) -> Tuple[torch.Tensor, ...]:
+        emb = self.linear(F.silu(temb))
+        emb = M.gather_from_tensor_model_parallel_region(emb, ps.get_tensor_model_parallel_group())
+        return emb.chunk(self.n_chunks, dim=1)
+
+
+class ParallelMLP(nn.Module):
+    """``linear_fc1`` (column-parallel) -> activation -> ``linear_fc2`` (row-parallel)."""
+
+    def __init__(self, dim: int, hidden: int, activation: str, tp: int = 1, device=None, dtype=None):
+        super().__init__()
+        self.activation = activation
+        self.linear_fc1 = ColumnParallelLinear(dim, hidden, tp=tp, device=device, dtype=dtype)
+        self.linear_fc2 = RowParallelLinear(hidden, dim, tp=tp, device=device, dtype=dtype)
+
+    def forward_gate_residual(self, x, gate, residual):
+        h = self.linear_fc1(x, activation=self.activation)
+        return self.linear_fc2.forward_gate_residual(h, gate, residual)
+
+
+# ---------------------------------------------------------------------------------------------
+# Attention with Ulysses context parallelism
+# ---------------------------------------------------------------------------------------------
+
+def _ulysses_attention(q, k, v, tq, tk, tv, pad: Optional[SeqPad], kv_valid_len: Optional[int]):
+    """Joint attention over ``cat(video, text)`` with the Ulysses exchange.
+
+    ``q, k, v``: video ``[B, H/tp, s, D]`` (sequence-sharded over CP); ``tq, tk, tv``: text
+    ``[B, H/tp, T, D]`` (replicated over CP).  Returns token-major video ``[B, s, H/tp*D]``
+    and text ``[B, T, H/tp*D]`` (call sites X1-X4 of the reference:
+    ``dit_attention.py:275-297, 321-327``).
+    """
+    cp_group = ps.get_context_parallel_group()
+    cp = ps.get_context_parallel_world_size()
+    T = tq.shape[2]
+    if cp > 1:
+        q = M.ulysses_scatter_heads(q, cp_group)
+        k = M.ulysses_scatter_heads(k, cp_group)
+        v = M.ulysses_scatter_heads(v, cp_group)
+        tq = M.split_forward_gather_backward(tq, cp_group, dim=1, grad_scale="down")
+        tk = M.split_forward_gather_backward(tk, cp_group, dim=1, grad_scale="down")
+        tv = M.split_forward_gather_backward(tv, cp_group, dim=1, grad_scale="down")
+        if pad is not None and pad.pad:
+            q, k, v = (pad.remove(t, 2) for t in (q, k, v))
+    S = q.shape[2]
+    o = ops.attention(torch.cat([q, tq], dim=2), torch.cat([k, tk], dim=2), torch.cat([v, tv], dim=2),
+                      kv_valid_len=None if kv_valid_len is None else S + kv_valid_len)
+    o_v, o_t = o[:, :S], o[:, S:]
+    if cp > 1:
+        B, _, hd = o_v.shape
+        D = q.shape[-1]
+        if pad is not None and pad.pad:
+            o_v = pad.add(o_v, 1)
+        o_v = M.ulysses_gather_heads(o_v.reshape(B, o_v.shape[1], hd // D, D).transpose(1, 2), cp_group)
+        o_v = o_v.transpose(1, 2).reshape(B, -1, cp * hd)
+        o_t = M.gather_forward_split_backward(o_t.contiguous(), cp_group, dim=2, grad_scale="up")
+    return o_v, o_t.reshape(o_t.shape[0], T, -1)
+
+
+class JointAttention(nn.Module):
+    """Dual-stream attention: separate QKV / out projections for video and text tokens."""
+
+    def __init__(self, dim: int, heads: int, head_dim: int, tp: int, eps: float, qkv_bias: bool = True,
+                 device=None, dtype=None):
+        super().__init__()
+        kw = dict(device=device, dtype=dtype)
+        self.heads_local, self.head_dim, self.eps = heads // tp, head_dim, eps
+        self.linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, **kw)
+        self.added_linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, **kw)
+        self.linear_proj = RowParallelLinear(dim, dim, tp=tp, **kw)
+        self.added_linear_proj = RowParallelLinear(dim, dim, tp=tp, **kw)
+        self.q_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
+        self.k_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
+        self.added_q_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
+        self.added_k_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
+
+    def forward(self, x, ctx, cos, sin, pad, kv_valid_len):
+        tpg = ps.get_tensor_model_parallel_group()
+        x = M.copy_to_tensor_model_parallel_region(x, tpg)
+        ctx = M.copy_to_tensor_model_parallel_region(ctx, tpg)
+        q, k, v = ops.qkv_projection(x, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight,
+                                     self.k_layernorm.weight, cos, sin, self.heads_local, self.eps)
+        tq, tk, tv = ops.qkv_projection(ctx, self.added_linear_qkv.weight, self.added_linear_qkv.bias,
+                                        self.added_q_layernorm.weight, self.added_k_layernorm.weight,
+                                        None, None, self.heads_local, self.eps)
+        return _ulysses_attention(q, k, v, tq, tk, tv, pad, kv_valid_len)
+
+
+class SingleAttention(nn.Module):
+    """Single-stream attention: one QKV over ``cat(video, text)``; no output projection."""
+
+    def __init__(self, dim: int, heads: int, head_dim: int, tp: int, eps: float, qkv_bias: bool = True,
+                 device=None, dtype=None):
+        super().__init__()
+        kw = dict(device=device, dtype=dtype)
+        self.heads_local, self.head_dim, self.eps = heads // tp, head_dim, eps
+        self.linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, **kw)
+        self.q_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
+        self.k_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
+
+    def forward(self, h, text_len, cos, sin, pad, kv_valid_len):
+        h = M.copy_to_tensor_model_parallel_region(h, ps.get_tensor_model_parallel_group())
+        s = h.shape[1] - text_len
+        q, k, v = ops.qkv_projection(h, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight,
+                                     self.k_layernorm.weight, cos, sin, self.heads_local, self.eps, rope_len=s)
+        return _ulysses_attention(q[:, :, :s], k[:, :, :s], v[:, :, :s], q[:, :, s:], k[:, :, s:], v[:, :, s:],
+                                  pad, kv_valid_len)
+
+
+# ---------------------------------------------------------------------------------------------
+# Blocks
+# ---------------------------------------------------------------------------------------------
+
+class HunyuanDiTLayer(nn.Module):
+    """Dual-stream block: video and text keep separate weights and meet in attention."""
+
+    def __init__(self, cfg, tp: int = 1, device=None, dtype=None):
+        super().__init__()
+        kw = dict(device=device, dtype=dtype)
+        H = cfg.hidden_size
+        self.eps = cfg.layernorm_epsilon
+        self.norm1 = AdaLNModulation(H, 6, tp, **kw)
+        self.norm1_context = AdaLNModulation(H, 6, tp, **kw)
+        self.self_attention = JointAttention(H, cfg.num_attention_heads, cfg.attention_head_dim, tp, self.eps,
+                                             cfg.add_qkv_bias, **kw)
+        self.mlp = ParallelMLP(H, cfg.mlp_hidden, cfg.dual_mlp_activation, tp, **kw)
+        self.ff_context = ParallelMLP(H, cfg.mlp_hidden, cfg.dual_mlp_activation, tp, **kw)
+
+    def forward(self, x, ctx, temb, cos, sin, pad: Optional[SeqPad] = None, kv_valid_len: Optional[int] = None):
+        shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.norm1(temb)
+        c_shift_msa, c_scale_msa, c_gate_msa, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(temb)
+        xn = ops.layernorm_modulate(x, scale_msa, shift_msa, self.eps)
+        cn = ops.layernorm_modulate(ctx, c_scale_msa, c_shift_msa, self.eps)
+        attn, c_attn = self.self_attention(xn, cn, cos, sin, pad, kv_valid_len)
+        x = self.self_attention.linear_proj.forward_gate_residual(attn, gate_msa, x)
+        ctx = self.self_attention.added_linear_proj.forward_gate_residual(c_attn, c_gate_msa, ctx)
+        xn = ops.layernorm_modulate(x, scale_mlp, shift_mlp, self.eps)
+        cn = ops.layernorm_modulate(ctx, c_scale_mlp, c_shift_mlp, self.eps)
+        x = self.mlp.forward_gate_residual(xn, gate_mlp, x)
+        ctx = self.ff_context.forward_gate_residual(cn, c_gate_mlp, ctx)
+        return x, ctx
+
+
+class HunyuanSingleDiTLayer(nn.Module):
+    """Single-stream block: one set of weights over ``cat(video, text)``; attention and MLP
+    run in parallel and are merged by one projection."""
+
+    def __init__(self, cfg, tp: int = 1, device=None, dtype=None):
+        super().__init__()
+        kw = dict(device=device, dtype=dtype)
+        H = cfg.hidden_size
+        self.eps = cfg.layernorm_epsilon
+        self.activation = cfg.single_mlp_activation
+        self.norm = AdaLNModulation(H, 3, tp, **kw)
+        self.proj_mlp = ColumnParallelLinear(H, cfg.mlp_hidden, tp=tp, **kw)
+        self.self_attention = SingleAttention(H, cfg.num_attention_heads, cfg.attention_head_dim, tp, self.eps,
+                                              cfg.add_qkv_bias, **kw)
+        self.proj_out = RowParallelLinear(H + cfg.mlp_hidden, H, tp=tp, input_partitions=(H, cfg.mlp_hidden), **kw)
+
+    def forward(self, x, ctx, temb, cos, sin, pad: Optional[SeqPad] = None, kv_valid_len: Optional[int] = None):
+        T = ctx.shape[1]
+        h = torch.cat([x, ctx], dim=1)
+        shift, scale, gate = self.norm(temb)
+        hn = ops.layernorm_modulate(h, scale, shift, self.eps)
+        mlp = self.proj_mlp(hn, activation=self.activation)
+        attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len)
+        merged = torch.cat([torch.cat([attn, c_attn], dim=1), mlp], dim=2)
+        h = self.proj_out.forward_gate_residual(merged, gate, h)
+        return h[:, :-T], h[:, -T:]
+
+
+class AdaLNContinuous(nn.Module):
+    """Output head norm: ``LN(x) * (1 + scale) + shift`` with ``(scale, shift) = Linear(SiLU(temb))``
+    (``dit_layerspec.py:55-78``; the linear is ``adaLN_modulation.1``)."""
+
+    def __init__(self, dim: int, cond_dim: int, eps: float = 1e-6, device=None, dtype=None):
+        super().__init__()
+        self.eps = eps
+        self.adaLN_modulation = nn.Sequential(nn.SiLU(), nn.Linear(cond_dim, 2 * dim, device=device, dtype=dtype))
+
+    def forward(self, x, temb):
+        scale, shift = self.adaLN_modulation(temb).chunk(2, dim=1)
+        return ops.layernorm_modulate(x, scale, shift, self.eps)

@@ -1,0 +1,287 @@
+"""Process-group topology for mixed DP / TP / Ulysses-CP training plus encoder ranks.
+
+Rank layout (identical to the reference so converted checkpoints and batch semantics
+carry over, ``teletron/core/parallel_state.py:299-302, 348-357, 378-379, 468-471``):
+
+* DiT ranks are ``0 .. dit_world-1``; encoder-service ranks sit at the tail.
+* Inside the DiT world: tensor-parallel fastest, then context-parallel, then
+  data-parallel.  ``rank = dp * (tp*cp) + cp_idx * tp + tp_idx``.
+
+Differences from the reference, on purpose:
+
+* Every rank of the job (encoder ranks included) walks the *same* deterministic list
+  of ``new_group`` calls.  The reference creates caller-dependent groups and lets
+  encoder ranks skip ~20 creations (``parallel_state.py:130-135, 162-167``), which is
+  only safe by accident of the store implementation.
+* No patching of ``torch.distributed`` defaults (``parallel_state.py:39-86``): callers
+  get explicit group handles.
+* Works un-initialised: with no process group every size is 1 and every group ``None``,
+  so single-process runs need no ``torch.distributed`` at all.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import datetime
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclasses.dataclass
+class CommPair:
+    """One encoder-rank -> DiT-rank stream (``parallel_state.py:27-32``)."""
+    producer: int
+    consumer: int
+    dp_rank: int
+    dp_size: int
+
+
+@dataclasses.dataclass
+class _State:
+    world_size: int = 1
+    rank: int = 0
+    dit_world_size: int = 1
+    encoder_world_size: int = 0
+    tp: int = 1
+    cp: int = 1
+    dp: int = 1
+    tp_rank: int = 0
+    cp_rank: int = 0
+    dp_rank: int = 0
+    is_dit_rank: bool = True
+    backend: Optional[str] = None
+    world_group: Optional[dist.ProcessGroup] = None
+    dit_group: Optional[dist.ProcessGroup] = None
+    tp_group: Optional[dist.ProcessGroup] = None
+    cp_group: Optional[dist.ProcessGroup] = None
+    dp_group: Optional[dist.ProcessGroup] = None
+    dp_cp_group: Optional[dist.ProcessGroup] = None
+    dp_cp_group_gloo: Optional[dist.ProcessGroup] = None
+    tp_cp_group: Optional[dist.ProcessGroup] = None
+    tp_ranks: List[int] = dataclasses.field(default_factory=lambda: [0])
+    cp_ranks: List[int] = dataclasses.field(default_factory=lambda: [0])
+    dp_ranks: List[int] = dataclasses.field(default_factory=lambda: [0])
+    dp_cp_ranks: List[int] = dataclasses.field(default_factory=lambda: [0])
+    tp_cp_ranks: List[int] = dataclasses.field(default_factory=lambda: [0])
+    comm_pairs: List[CommPair] = dataclasses.field(default_factory=list)
+    initialized: bool = False
+
+
+_STATE = _State()
+
+
+def rank_coords(rank: int, tp: int, cp: int) -> Dict[str, int]:
+    """Coordinates of a DiT rank: tp fastest, then cp, then dp."""
+    return {"tp": rank % tp, "cp": (rank // tp) % cp, "dp": rank // (tp * cp)}
+
+
+def build_rank_lists(dit_world: int, tp: int, cp: int) -> Dict[str, List[List[int]]]:
+    """All group memberships as plain lists (pure function; unit-testable without dist)."""
+    if dit_world % (tp * cp) != 0:
+        raise ValueError(f"DiT world size {dit_world} is not divisible by tp*cp = {tp}*{cp}")
+    dp = dit_world // (tp * cp)
+    block = tp * cp
+    tp_groups = [list(range(i * tp, (i + 1) * tp)) for i in range(dit_world // tp)]
+    cp_groups = [[d * block + c * tp + t for c in range(cp)] for d in range(dp) for t in range(tp)]
+    dp_groups = [[d * block + j for d in range(dp)] for j in range(block)]
+    # data-parallel "with context parallel": all ranks sharing a tp index
+    dp_cp_groups = [[d * block + c * tp + t for d in range(dp) for c in range(cp)] for t in range(tp)]
+    tp_cp_groups = [list(range(d * block, (d + 1) * block)) for d in range(dp)]
+    return {"tp": tp_groups, "cp": cp_groups, "dp": dp_groups, "dp_cp": dp_cp_groups, "tp_cp": tp_cp_groups}
+
+
+def build_comm_pairs(dit_world: int, encoder_world: int, tp: int, cp: int) -> List[CommPair]:
+    """Producer/consumer pairing (``parallel_state.py:174-205``).
+
+    The consumers are the first rank of every TP x CP block (one per data-parallel
+    replica); consumer ``i`` is served by encoder rank ``dit_world + i % encoder_world``.
+    """
+    if encoder_world == 0:
+        return []
+    block = tp * cp
+    dp = dit_world // block
+    pairs = []
+    for d in range(dp):
+        consumer = d * block
+        pairs.append(CommPair(producer=dit_world + d % encoder_world, consumer=consumer,
+                              dp_rank=d, dp_size=dp))
+    return pairs
+
+
+def _new_group(ranks, backend=None, timeout=None):
+    kwargs = {}
+    if timeout is not None:
+        kwargs["timeout"] = timeout
+    return dist.new_group(ranks=ranks, backend=backend, **kwargs)
+
+
+def initialize_model_parallel(tensor_model_parallel_size: int = 1, context_parallel_size: int = 1,
+                              encoder_world_size: int = 0, timeout_minutes: Optional[float] = None,
+                              create_gloo_groups: bool = True) -> None:
+    """Create every group.  Must be called by all ranks of the default process group."""
+    global _STATE
+    if not dist.is_initialized():
+        if tensor_model_parallel_size * context_parallel_size != 1 or encoder_world_size:
+            raise RuntimeError("torch.distributed is not initialised but parallel sizes > 1 were requested")
+        _STATE = _State(initialized=True)
+        return
+    world = dist.get_world_size()
+    rank = dist.get_rank()
+    tp, cp = tensor_model_parallel_size, context_parallel_size
+    dit_world = world - encoder_world_size
+    if dit_world <= 0:
+        raise ValueError("encoder ranks consume the whole world")
+    lists = build_rank_lists(dit_world, tp, cp)
+    timeout = datetime.timedelta(minutes=timeout_minutes) if timeout_minutes else None
+    backend = dist.get_backend()
+    st = _State(world_size=world, rank=rank, dit_world_size=dit_world, encoder_world_size=encoder_world_size,
+                tp=tp, cp=cp, dp=dit_world // (tp * cp), is_dit_rank=rank < dit_world, backend=backend)
+    st.world_group = dist.group.WORLD
+    if encoder_world_size > 0:
+        st.dit_group = _new_group(list(range(dit_world)), timeout=timeout)
+    else:
+        st.dit_group = dist.group.WORLD
+
+    def make(kind: str, attr_group: str, attr_ranks: str, gloo_attr: Optional[str] = None):
+        for ranks in lists[kind]:
+            if len(ranks) == 1:
+                # a singleton group needs no communicator; keep the handle None
+                if rank in ranks:
+                    setattr(st, attr_ranks, ranks)
+                continue
+            g = _new_group(ranks, timeout=timeout)
+            g_gloo = _new_group(ranks, backend="gloo", timeout=timeout) if (gloo_attr and create_gloo_groups
+                                                                             and backend != "gloo") else None
+            if rank in ranks:
+                setattr(st, attr_group, g)
+                setattr(st, attr_ranks, ranks)
+                if gloo_attr:
+                    setattr(st, gloo_attr, g_gloo if g_gloo is not None else g)
+
+    make("tp", "tp_group", "tp_ranks")
+    make("cp", "cp_group", "cp_ranks")
+    make("dp", "dp_group", "dp_ranks")
+    make("dp_cp", "dp_cp_group", "dp_cp_ranks", "dp_cp_group_gloo")
+    make("tp_cp", "tp_cp_group", "tp_cp_ranks")
+    if st.is_dit_rank:
+        c = rank_coords(rank, tp, cp)
+        st.tp_rank, st.cp_rank, st.dp_rank = c["tp"], c["cp"], c["dp"]
+    st.comm_pairs = build_comm_pairs(dit_world, encoder_world_size, tp, cp)
+    st.initialized = True
+    _STATE = st
+
+
+def destroy_model_parallel() -> None:
+    global _STATE
+    _STATE = _State()
+
+
+def model_parallel_is_initialized() -> bool:
+    return _STATE.initialized
+
+
+def state() -> _State:
+    return _STATE
+
+
+# ---- getters with the reference's public names (parallel_state.py:546-585) -----------------
+
+def get_world_group():
+    return _STATE.world_group
+
+
+def get_transformer_model_group():
+    return _STATE.dit_group
+
+
+def get_tensor_model_parallel_group():
+    return _STATE.tp_group
+
+
+def get_tensor_model_parallel_world_size() -> int:
+    return _STATE.tp
+
+
+def get_tensor_model_parallel_rank() -> int:
+    return _STATE.tp_rank
+
+
+def get_context_parallel_group():
+    return _STATE.cp_group
+
+
+def get_context_parallel_world_size() -> int:
+    return _STATE.cp
+
+
+def get_context_parallel_rank() -> int:
+    return _STATE.cp_rank
+
+
+def get_data_parallel_group(with_context_parallel: bool = False):
+    return _STATE.dp_cp_group if with_context_parallel else _STATE.dp_group
+
+
+def get_data_parallel_group_gloo(with_context_parallel: bool = True):
+    return _STATE.dp_cp_group_gloo
+
+
+def get_data_parallel_world_size(with_context_parallel: bool = False) -> int:
+    return _STATE.dp * _STATE.cp if with_context_parallel else _STATE.dp
+
+
+def get_data_parallel_rank(with_context_parallel: bool = False) -> int:
+    if with_context_parallel:
+        return _STATE.dp_rank * _STATE.cp + _STATE.cp_rank
+    return _STATE.dp_rank
+
+
+def get_data_parallel_ranks(with_context_parallel: bool = False) -> List[int]:
+    return _STATE.dp_cp_ranks if with_context_parallel else _STATE.dp_ranks
+
+
+def get_tensor_context_parallel_group():
+    return _STATE.tp_cp_group
+
+
+def get_tensor_context_parallel_world_size() -> int:
+    return _STATE.tp * _STATE.cp
+
+
+def get_tensor_context_parallel_rank() -> int:
+    return _STATE.cp_rank * _STATE.tp + _STATE.tp_rank
+
+
+def get_tensor_context_parallel_src_rank() -> int:
+    """Global rank of the first member of this rank's TP x CP block."""
+    return _STATE.tp_cp_ranks[0]
+
+
+def is_dit_rank() -> bool:
+    return _STATE.is_dit_rank
+
+
+def get_comm_pairs() -> List[CommPair]:
+    return list(_STATE.comm_pairs)
+
+
+def get_comm_pair() -> Optional[CommPair]:
+    """The pair this DiT rank consumes from (None for non-src ranks or without encoder ranks)."""
+    for p in _STATE.comm_pairs:
+        if p.consumer == _STATE.rank:
+            return p
+    return None
+
+
+def get_producer_pairs() -> List[CommPair]:
+    """All pairs served by this encoder rank."""
+    return [p for p in _STATE.comm_pairs if p.producer == _STATE.rank]
+
+
+def local_device() -> torch.device:
+    if torch.cuda.is_available():
+        return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")) % max(torch.cuda.device_count(), 1))
+    return torch.device("cpu")

@@ -1,0 +1,58 @@
+"""End-to-end training on CPU ranks (gloo): the tiny MMDiT with Ulysses CP=2, ZeRO-1 AdamW, logging,
+checkpoint save and bit-exact resume."""
+
+import json
+import os
+
+import torch
+
+from dist_utils import run_distributed
+
+EXAMPLE = os.path.join(os.path.dirname(__file__), "..", "examples", "hunyuanvideo")
+
+
+def _train(rank, world, tmp, extra, iters, load):
+    import sys
+    sys.path.insert(0, EXAMPLE)
+    import importlib
+    import pretrain_hunyuanvideo as entry
+    importlib.reload(entry)
+    from teletron_b200.training import pretrain
+    os.environ["TELETRON_B200_KEEP_PG"] = "1"
+    log = os.path.join(tmp, f"log_{iters}_{int(load)}.jsonl")
+    argv = ["--model-size", "tiny", "--dataset-type", "FakeDataset", "--num-frames", "9", "--video-resolution", "64", "64",
+            "--text-len", "16", "--train-iters", str(iters), "--lr", "1e-4", "--use-distributed-optimizer",
+            "--num-workers", "0", "--save", os.path.join(tmp, "ckpt"), "--save-interval", "5", "--jsonl-log", log] + extra
+    if load:
+        argv += ["--load", os.path.join(tmp, "ckpt")]
+    model = pretrain(entry.train_valid_test_datasets_provider, entry.model_provider, entry.forward_step,
+                     extra_args_provider=entry.extra_args_provider, argv=argv)
+    flat = torch.cat([p.detach().float().reshape(-1) for p in model.module.transformer.parameters()])
+    return flat, (open(log).read() if rank == 0 else "")
+
+
+def test_tiny_mmdit_cp2_ten_steps_and_resume(tmp_path):
+    tmp = str(tmp_path)
+    extra = ["--context-parallel-size", "2"]
+    full = run_distributed(_train, 2, tmp, extra, 10, False)
+    lines = [json.loads(l) for l in full[0][1].strip().splitlines()]
+    assert len(lines) == 10 and all("loss" in l for l in lines)
+    assert lines[-1]["loss"] < lines[0]["loss"] * 1.5       # finite, sane
+    torch.testing.assert_close(full[0][0], full[1][0], rtol=0, atol=0)      # CP ranks hold identical weights
+    assert os.path.isfile(os.path.join(tmp, "ckpt", "iter_0000005", "mp_rank_00", "model_optim_rng.pt"))
+    assert open(os.path.join(tmp, "ckpt", "latest_checkpointed_iteration.txt")).read().strip() == "10"
+    # resume from iteration 5 and run to 10: must land on exactly the same weights
+    with open(os.path.join(tmp, "ckpt", "latest_checkpointed_iteration.txt"), "w") as f:
+        f.write("5")
+    resumed = run_distributed(_train, 2, tmp, extra, 10, True)
+    torch.testing.assert_close(resumed[0][0], full[0][0], rtol=0, atol=0)
+
+
+def test_tp2_matches_cp2_loss_curve(tmp_path):
+    """The reference's run_test_cases.sh compares TP1CP2 against TP2CP1 by eye; here it is asserted."""
+    a = run_distributed(_train, 2, str(tmp_path / "a"), ["--context-parallel-size", "2", "--sanity-check"], 4, False)
+    b = run_distributed(_train, 2, str(tmp_path / "b"), ["--tensor-model-parallel-size", "2", "--sanity-check"], 4, False)
+    la = [json.loads(l)["loss"] for l in a[0][1].strip().splitlines()]
+    lb = [json.loads(l)["loss"] for l in b[0][1].strip().splitlines()]
+    for x, y in zip(la, lb):
+        assert abs(x - y) < 2e-4 * max(1.0, abs(x))
