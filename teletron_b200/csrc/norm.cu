@@ -1,0 +1,482 @@
+// LayerNorm(no affine) + AdaLN modulation, optionally fused with the gated residual update,
+// forward and backward; plain RMSNorm forward and backward.
+//
+// Covers what the reference's `teletron_op/fused_adaln` (adaln_forward.cu:111-196,
+// adaln_backward.cu:62-127, scale_shift_backward.cu:49-126) and `fused_rmsnorm` extensions do,
+// without their restrictions: any column count that is a multiple of 8 up to 8192, any row
+// count, per-batch modulation vectors, fp32 arithmetic throughout, (mean, rstd) saved instead of
+// a normalised copy of the activations, and every launch on the caller's stream.
+#include "common.cuh"
+#include "teletron_b200.h"
+
+namespace {
+
+using namespace tt;
+
+constexpr int kMaxCols = 8192;
+
+// ---------------------------------------------------------------------------------------------
+// forward: one warp per row, the row lives in registers
+// ---------------------------------------------------------------------------------------------
+template <int VPL, bool GATE>
+__global__ void __launch_bounds__(256) ln_mod_fwd_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ branch,
+    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ scale,
+    const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ new_res,
+    __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+    long rows, int cols, long rows_per_batch, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int nvec = cols >> 3;
+    const float inv_cols = 1.f / (float)cols;
+    for (long row = (long)blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows;
+         row += (long)gridDim.x * warps_per_cta) {
+        const long b = row / rows_per_batch;
+        const __nv_bfloat16* xr = x + row * cols;
+        float v[VPL][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = lane + i * 32;
+            if (c < nvec) {
+                unpack8(ld8(xr + c * 8), v[i]);
+                if (GATE) {
+                    float br[8], g[8];
+                    unpack8(ld8(branch + row * cols + c * 8), br);
+                    unpack8(ld8(gate + b * cols + c * 8), g);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] + g[j] * br[j];
+                    // the residual stream is stored in bf16: normalise exactly what is stored
+                    bf16x8 packed = pack8(v[i]);
+                    st8(new_res + row * cols + c * 8, packed);
+                    unpack8(packed, v[i]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum += v[i][j];
+            }
+        }
+        const float mean = warp_sum(sum) * inv_cols;
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            if (lane + i * 32 < nvec) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float d = v[i][j] - mean;
+                    sq += d * d;
+                }
+            }
+        }
+        const float rstd = rsqrtf(warp_sum(sq) * inv_cols + eps);
+        if (lane == 0) {
+            mean_out[row] = mean;
+            rstd_out[row] = rstd;
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = lane + i * 32;
+            if (c < nvec) {
+                float sc[8], sh[8], o[8];
+                unpack8(ld8(scale + b * cols + c * 8), sc);
+                unpack8(ld8(shift + b * cols + c * 8), sh);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * (1.f + sc[j]) + sh[j];
+                st8(y + row * cols + c * 8, pack8(o));
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward: one CTA walks rows, thread t owns columns [8t, 8t+8); column sums stay in registers
+// ---------------------------------------------------------------------------------------------
+// partials layout: [batch][blocks_per_batch][K][cols] fp32 with K = 2 (dscale, dshift) or 3 (+dgate)
+template <bool GATE, int MAXT>
+__global__ void __launch_bounds__(MAXT) ln_mod_bwd_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ dres_in,
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ branch,
+    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ scale,
+    const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+    __nv_bfloat16* __restrict__ dbranch, float* __restrict__ partials, int cols, long rows_per_batch) {
+    __shared__ float red[64];
+    const int nvec = cols >> 3;
+    const int t = threadIdx.x;
+    const bool active = t < nvec;
+    const long b = blockIdx.y;
+    const float inv_cols = 1.f / (float)cols;
+    float sc1[8], gt[8];
+    float acc_scale[8], acc_shift[8], acc_gate[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        sc1[j] = 0.f;
+        gt[j] = 0.f;
+        acc_scale[j] = acc_shift[j] = acc_gate[j] = 0.f;
+    }
+    if (active) {
+        unpack8(ld8(scale + b * cols + t * 8), sc1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc1[j] += 1.f;
+        if (GATE) unpack8(ld8(gate + b * cols + t * 8), gt);
+    }
+    for (long r = blockIdx.x; r < rows_per_batch; r += gridDim.x) {
+        const long row = b * rows_per_batch + r;
+        float g[8], xh[8], dyv[8];
+        float s1 = 0.f, s2 = 0.f;
+        const float mu = mean[row], rs = rstd[row];
+        if (active) {
+            float xv[8];
+            unpack8(ld8(dy + row * cols + t * 8), dyv);
+            unpack8(ld8(x + row * cols + t * 8), xv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                xh[j] = (xv[j] - mu) * rs;
+                g[j] = dyv[j] * sc1[j];
+                s1 += g[j];
+                s2 += g[j] * xh[j];
+                acc_scale[j] += dyv[j] * xh[j];
+                acc_shift[j] += dyv[j];
+            }
+        }
+        const float2 s = block_sum2(s1, s2, red);
+        if (active) {
+            const float m1 = s.x * inv_cols, m2 = s.y * inv_cols;
+            float d[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d[j] = rs * (g[j] - m1 - xh[j] * m2);
+            if (dres_in != nullptr) {
+                float up[8];
+                unpack8(ld8(dres_in + row * cols + t * 8), up);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) d[j] += up[j];
+            }
+            st8(dx + row * cols + t * 8, pack8(d));
+            if (GATE) {
+                float br[8], db[8];
+                unpack8(ld8(branch + row * cols + t * 8), br);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc_gate[j] += d[j] * br[j];
+                    db[j] = d[j] * gt[j];
+                }
+                st8(dbranch + row * cols + t * 8, pack8(db));
+            }
+        }
+    }
+    if (active) {
+        constexpr int K = GATE ? 3 : 2;
+        float* p = partials + ((b * gridDim.x + blockIdx.x) * K) * (long)cols + t * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            p[j] = acc_scale[j];
+            p[cols + j] = acc_shift[j];
+            if (GATE) p[2 * cols + j] = acc_gate[j];
+        }
+    }
+}
+
+// out[k][b][c] (bf16) = sum over blocks of partials[b][blk][k][c]
+__global__ void column_finalize_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ out0,
+                                       __nv_bfloat16* __restrict__ out1, __nv_bfloat16* __restrict__ out2, int K,
+                                       int nblk, int cols) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int k = blockIdx.y;
+    const long b = blockIdx.z;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int i = 0; i < nblk; ++i) s += partials[((b * nblk + i) * K + k) * (long)cols + c];
+    __nv_bfloat16* o = k == 0 ? out0 : (k == 1 ? out1 : out2);
+    if (o != nullptr) o[b * cols + c] = __float2bfloat16(s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// gated residual: out = res + gate[b] * branch (+ backward with the gate's column sums)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gate_residual_fwd_kernel(const __nv_bfloat16* __restrict__ res,
+                                                               const __nv_bfloat16* __restrict__ branch,
+                                                               const __nv_bfloat16* __restrict__ gate,
+                                                               __nv_bfloat16* __restrict__ out, long rows, int cols,
+                                                               long rows_per_batch) {
+    const int nvec = cols >> 3;
+    const long total = rows * nvec;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long row = i / nvec;
+        const int c = (int)(i - row * nvec);
+        const long b = row / rows_per_batch;
+        float r[8], br[8], g[8];
+        unpack8(ld8(res + i * 8), r);
+        unpack8(ld8(branch + i * 8), br);
+        unpack8(ld8(gate + b * cols + c * 8), g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] += g[j] * br[j];
+        st8(out + i * 8, pack8(r));
+    }
+}
+
+// dbranch = gate * dout; partial dgate column sums of dout * branch (K = 1 partial layout)
+__global__ void __launch_bounds__(1024) gate_residual_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
+                                                                const __nv_bfloat16* __restrict__ branch,
+                                                                const __nv_bfloat16* __restrict__ gate,
+                                                                __nv_bfloat16* __restrict__ dbranch,
+                                                                float* __restrict__ partials, int cols,
+                                                                long rows_per_batch) {
+    const int nvec = cols >> 3;
+    const int t = threadIdx.x;
+    if (t >= nvec) return;
+    const long b = blockIdx.y;
+    float gt[8], acc[8];
+    unpack8(ld8(gate + b * cols + t * 8), gt);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (long r = blockIdx.x; r < rows_per_batch; r += gridDim.x) {
+        const long row = b * rows_per_batch + r;
+        float d[8], br[8], db[8];
+        unpack8(ld8(dout + row * cols + t * 8), d);
+        unpack8(ld8(branch + row * cols + t * 8), br);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            acc[j] += d[j] * br[j];
+            db[j] = d[j] * gt[j];
+        }
+        st8(dbranch + row * cols + t * 8, pack8(db));
+    }
+    float* p = partials + (b * gridDim.x + blockIdx.x) * (long)cols + t * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] = acc[j];
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm over the last dimension (any cols % 8 == 0 up to 8192): y = x * rstd * w
+// ---------------------------------------------------------------------------------------------
+template <int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
+                                                         long rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int wpc = blockDim.x >> 5;
+    const int nvec = cols >> 3;
+    for (long row = (long)blockIdx.x * wpc + (threadIdx.x >> 5); row < rows; row += (long)gridDim.x * wpc) {
+        float v[VPL][8];
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = lane + i * 32;
+            if (c < nvec) {
+                unpack8(ld8(x + row * cols + c * 8), v[i]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sq += v[i][j] * v[i][j];
+            }
+        }
+        const float rstd = rsqrtf(warp_sum(sq) / (float)cols + eps);
+        if (lane == 0) rstd_out[row] = rstd;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = lane + i * 32;
+            if (c < nvec) {
+                float wv[8], o[8];
+                unpack8(ld8(w + c * 8), wv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
+                st8(y + row * cols + c * 8, pack8(o));
+            }
+        }
+    }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)); partial dw[c] = sum_rows dy * xhat  (uses the saved INPUT,
+// not y / w as the reference does, so zero weights are harmless)
+__global__ void __launch_bounds__(1024) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                          const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ w,
+                                                          const float* __restrict__ rstd,
+                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ partials,
+                                                          long rows, int cols) {
+    __shared__ float red[64];
+    const int nvec = cols >> 3;
+    const int t = threadIdx.x;
+    const bool active = t < nvec;
+    float wv[8], acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        wv[j] = 0.f;
+        acc[j] = 0.f;
+    }
+    if (active) unpack8(ld8(w + t * 8), wv);
+    for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+        float g[8], xh[8];
+        float s = 0.f;
+        const float rs = rstd[row];
+        if (active) {
+            float d[8], xv[8];
+            unpack8(ld8(dy + row * cols + t * 8), d);
+            unpack8(ld8(x + row * cols + t * 8), xv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                xh[j] = xv[j] * rs;
+                g[j] = d[j] * wv[j];
+                s += g[j] * xh[j];
+                acc[j] += d[j] * xh[j];
+            }
+        }
+        const float m = block_sum(s, red) / (float)cols;
+        if (active) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = rs * (g[j] - xh[j] * m);
+            st8(dx + row * cols + t * 8, pack8(o));
+        }
+    }
+    if (active) {
+        float* p = partials + (long)blockIdx.x * cols + t * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) p[j] = acc[j];
+    }
+}
+
+inline int pick_blocks(long rows_per_batch, int batch) {
+    long want = (148L * 4) / (batch > 0 ? batch : 1);
+    if (want < 1) want = 1;
+    if (want > rows_per_batch) want = rows_per_batch;
+    if (want > TT_NORM_MAX_PARTIAL_BLOCKS) want = TT_NORM_MAX_PARTIAL_BLOCKS;
+    return (int)want;
+}
+
+inline bool bad_cols(int cols) { return cols <= 0 || (cols & 7) || cols > kMaxCols; }
+
+}  // namespace
+
+extern "C" int tt_norm_partial_blocks(long rows_per_batch, int batch) { return pick_blocks(rows_per_batch, batch); }
+
+#define LAUNCH_FWD(VPL)                                                                                         \
+    do {                                                                                                        \
+        if (has_gate)                                                                                           \
+            ln_mod_fwd_kernel<VPL, true><<<grid, 256, 0, st>>>(X, BR, G, SC, SH, NR, Y, mean, rstd, rows, cols, \
+                                                               rows_per_batch, eps);                            \
+        else                                                                                                    \
+            ln_mod_fwd_kernel<VPL, false><<<grid, 256, 0, st>>>(X, BR, G, SC, SH, NR, Y, mean, rstd, rows,      \
+                                                                cols, rows_per_batch, eps);                     \
+    } while (0)
+
+extern "C" int tt_ln_mod_fwd(const void* x, const void* branch, const void* gate, const void* scale,
+                             const void* shift, void* new_res, void* y, float* mean, float* rstd, long rows,
+                             int cols, long rows_per_batch, float eps, void* stream) {
+    if (bad_cols(cols) || rows <= 0 || rows_per_batch <= 0 || rows % rows_per_batch) return TT_ERR_ARG;
+    const bool has_gate = branch != nullptr;
+    if (has_gate && (gate == nullptr || new_res == nullptr)) return TT_ERR_ARG;
+    auto X = (const __nv_bfloat16*)x;
+    auto BR = (const __nv_bfloat16*)branch;
+    auto G = (const __nv_bfloat16*)gate;
+    auto SC = (const __nv_bfloat16*)scale;
+    auto SH = (const __nv_bfloat16*)shift;
+    auto NR = (__nv_bfloat16*)new_res;
+    auto Y = (__nv_bfloat16*)y;
+    cudaStream_t st = (cudaStream_t)stream;
+    long want = (rows + 7) / 8;
+    const int grid = (int)(want < 148L * 16 ? want : 148L * 16);
+    const int vpl = ((cols >> 3) + 31) / 32;
+    if (vpl <= 4) LAUNCH_FWD(4);
+    else if (vpl <= 8) LAUNCH_FWD(8);
+    else if (vpl <= 12) LAUNCH_FWD(12);
+    else if (vpl <= 16) LAUNCH_FWD(16);
+    else LAUNCH_FWD(32);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+extern "C" int tt_ln_mod_bwd(const void* dy, const void* dres_in, const void* x, const void* branch,
+                             const void* gate, const void* scale, const float* mean, const float* rstd, void* dx,
+                             void* dbranch, float* partials, void* dscale, void* dshift, void* dgate, long rows,
+                             int cols, long rows_per_batch, void* stream) {
+    if (bad_cols(cols) || rows <= 0 || rows_per_batch <= 0 || rows % rows_per_batch) return TT_ERR_ARG;
+    const bool has_gate = branch != nullptr;
+    if (has_gate && (gate == nullptr || dbranch == nullptr || dgate == nullptr)) return TT_ERR_ARG;
+    const int batch = (int)(rows / rows_per_batch);
+    const int nblk = pick_blocks(rows_per_batch, batch);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = (((cols >> 3) + 31) / 32) * 32;
+    dim3 grid(nblk, batch);
+#define LN_BWD(G_, T_)                                                                                          \
+    ln_mod_bwd_kernel<G_, T_><<<grid, threads, 0, st>>>(                                                        \
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres_in, (const __nv_bfloat16*)x,                       \
+        (const __nv_bfloat16*)branch, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)scale, mean, rstd,      \
+        (__nv_bfloat16*)dx, (__nv_bfloat16*)dbranch, partials, cols, rows_per_batch)
+    if (has_gate) {
+        if (threads <= 512) LN_BWD(true, 512);
+        else LN_BWD(true, 1024);
+    } else {
+        if (threads <= 512) LN_BWD(false, 512);
+        else LN_BWD(false, 1024);
+    }
+    TT_CHECK_LAUNCH();
+    const int K = has_gate ? 3 : 2;
+    dim3 fgrid((cols + 255) / 256, K, batch);
+    column_finalize_kernel<<<fgrid, 256, 0, st>>>(partials, (__nv_bfloat16*)dscale, (__nv_bfloat16*)dshift,
+                                                  (__nv_bfloat16*)dgate, K, nblk, cols);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+extern "C" int tt_gate_residual_fwd(const void* res, const void* branch, const void* gate, void* out, long rows,
+                                    int cols, long rows_per_batch, void* stream) {
+    if (bad_cols(cols) || rows <= 0 || rows_per_batch <= 0 || rows % rows_per_batch) return TT_ERR_ARG;
+    const long total = rows * (cols >> 3);
+    long want = (total + 255) / 256;
+    const int grid = (int)(want < 148L * 32 ? want : 148L * 32);
+    gate_residual_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)res, (const __nv_bfloat16*)branch, (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, rows,
+        cols, rows_per_batch);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+extern "C" int tt_gate_residual_bwd(const void* dout, const void* branch, const void* gate, void* dbranch,
+                                    float* partials, void* dgate, long rows, int cols, long rows_per_batch,
+                                    void* stream) {
+    if (bad_cols(cols) || rows <= 0 || rows_per_batch <= 0 || rows % rows_per_batch) return TT_ERR_ARG;
+    const int batch = (int)(rows / rows_per_batch);
+    const int nblk = pick_blocks(rows_per_batch, batch);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = (((cols >> 3) + 31) / 32) * 32;
+    gate_residual_bwd_kernel<<<dim3(nblk, batch), threads, 0, st>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)branch, (const __nv_bfloat16*)gate, (__nv_bfloat16*)dbranch,
+        partials, cols, rows_per_batch);
+    TT_CHECK_LAUNCH();
+    column_finalize_kernel<<<dim3((cols + 255) / 256, 1, batch), 256, 0, st>>>(partials, (__nv_bfloat16*)dgate, nullptr,
+                                                                             nullptr, 1, nblk, cols);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+#define LAUNCH_RMS(VPL) \
+    rmsnorm_fwd_kernel<VPL><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, cols, eps)
+
+extern "C" int tt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int cols, float eps,
+                              void* stream) {
+    if (bad_cols(cols) || rows <= 0) return TT_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    long want = (rows + 7) / 8;
+    const int grid = (int)(want < 148L * 16 ? want : 148L * 16);
+    const int vpl = ((cols >> 3) + 31) / 32;
+    if (vpl <= 1) LAUNCH_RMS(1);
+    else if (vpl <= 4) LAUNCH_RMS(4);
+    else if (vpl <= 12) LAUNCH_RMS(12);
+    else if (vpl <= 16) LAUNCH_RMS(16);
+    else LAUNCH_RMS(32);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+extern "C" int tt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                              float* partials, void* dw, long rows, int cols, void* stream) {
+    if (bad_cols(cols) || rows <= 0) return TT_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nblk = pick_blocks(rows, 1);
+    const int threads = (((cols >> 3) + 31) / 32) * 32;
+    rmsnorm_bwd_kernel<<<nblk, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                 (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols);
+    TT_CHECK_LAUNCH();
+    column_finalize_kernel<<<dim3((cols + 255) / 256, 1, 1), 256, 0, st>>>(partials, (__nv_bfloat16*)dw, nullptr, nullptr,
+                                                                         1, nblk, cols);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}

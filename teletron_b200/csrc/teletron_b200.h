@@ -1,0 +1,58 @@
+/* C ABI of libteletron_b200.so: hand-written sm_100a kernels reached from Python through ctypes.
+ *
+ * Conventions: every pointer is a device pointer unless stated; bf16 buffers are passed as void*;
+ * `stream` is a cudaStream_t; every function returns TT_OK (0) or a TT_ERR_* code and never
+ * allocates device memory (scratch buffers are passed in by the caller, who sizes them with the
+ * *_partial_* helpers). */
+#pragma once
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TT_NORM_MAX_PARTIAL_BLOCKS 1024
+#define TT_QKV_MAX_PARTIAL_WARPS 4736
+
+const char* tt_last_cuda_error(void);
+int tt_version(void);
+
+/* ---- LayerNorm + AdaLN modulation (optionally fused with the gated residual update) ---- */
+int tt_norm_partial_blocks(long rows_per_batch, int batch);
+int tt_ln_mod_fwd(const void* x, const void* branch, const void* gate, const void* scale, const void* shift,
+                  void* new_res, void* y, float* mean, float* rstd, long rows, int cols, long rows_per_batch,
+                  float eps, void* stream);
+/* partials: fp32 [batch][tt_norm_partial_blocks][2 or 3][cols] */
+int tt_ln_mod_bwd(const void* dy, const void* dres_in, const void* x, const void* branch, const void* gate,
+                  const void* scale, const float* mean, const float* rstd, void* dx, void* dbranch, float* partials,
+                  void* dscale, void* dshift, void* dgate, long rows, int cols, long rows_per_batch, void* stream);
+int tt_gate_residual_fwd(const void* res, const void* branch, const void* gate, void* out, long rows, int cols,
+                         long rows_per_batch, void* stream);
+int tt_gate_residual_bwd(const void* dout, const void* branch, const void* gate, void* dbranch, float* partials,
+                         void* dgate, long rows, int cols, long rows_per_batch, void* stream);
+int tt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int cols, float eps, void* stream);
+int tt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* partials,
+                   void* dw, long rows, int cols, void* stream);
+
+/* ---- QKV post-processing: split + QK-RMSNorm + RoPE + head-major layout ---- */
+int tt_qkv_partial_warps(long rows, int heads);
+int tt_qkv_post_fwd(const void* qkv, const void* qw, const void* kw, const float* cos_t, const float* sin_t, void* q,
+                    void* k, void* v, long rows, int heads, long seq_in, long seq_out, long out_offset, long rope_len,
+                    float eps, void* stream);
+/* partials: fp32 [tt_qkv_partial_warps][2][128] */
+int tt_qkv_post_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw, const void* kw,
+                    const float* cos_t, const float* sin_t, void* dqkv, float* partials, void* dqw, void* dkw,
+                    long rows, int heads, long seq_in, long seq_out, long out_offset, long rope_len, float eps,
+                    void* stream);
+
+/* ---- activations ---- */
+int tt_gelu_fwd(const void* u, void* y, long n, int kind, void* stream);   /* kind 0 = erf, 1 = tanh */
+int tt_gelu_bwd(const void* dy, const void* u, void* du, long n, int kind, void* stream);
+
+/* ---- optimizer ---- */
+int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, void* master_lo, long n,
+             int state_is_bf16, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale,
+             void* stream);
+
+#ifdef __cplusplus
+}
+#endif

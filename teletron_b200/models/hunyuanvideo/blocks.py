@@ -96,11 +96,6 @@ class RowParallelLinear(nn.Module):
         y = M.reduce_from_tensor_model_parallel_region(y, ps.get_tensor_model_parallel_group())
         return y if self.bias is None else y + self.bias
 
-    def forward_gate_residual(self, x: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        """``residual + gate * (x W^T + b)``: one fused GEMM epilogue when ``tp == 1``."""
-        if self.tp == 1:
-            return ops.linear_gate_residual(x, self.weight, self.bias, gate, residual)
-        return ops.gate_residual(residual, self.forward(x), gate)
 
 
 class RMSNorm(nn.Module):
@@ -148,14 +143,20 @@ class ParallelMLP(nn.Module):
         self.linear_fc1 = ColumnParallelLinear(dim, hidden, tp=tp, device=device, dtype=dtype)
         self.linear_fc2 = RowParallelLinear(hidden, dim, tp=tp, device=device, dtype=dtype)
 
-    def forward_gate_residual(self, x, gate, residual):
-        h = self.linear_fc1(x, activation=self.activation)
-        return self.linear_fc2.forward_gate_residual(h, gate, residual)
+    def forward(self, x):
+        return self.linear_fc2(self.linear_fc1(x, activation=self.activation))
 
 
 # ---------------------------------------------------------------------------------------------
 # Attention with Ulysses context parallelism
 # ---------------------------------------------------------------------------------------------
+
+def _joint_attention(q, k, v, text_len: int, kv_valid_len: Optional[int]):
+    """Single-rank case: q, k, v already hold ``cat(video, text)`` as ``[B, h, S + T, D]``."""
+    S = q.shape[2] - text_len
+    o = ops.attention(q, k, v, kv_valid_len=None if kv_valid_len is None else S + kv_valid_len)
+    return o[:, :S], o[:, S:]
+
 
 def _ulysses_attention(q, k, v, tq, tk, tv, pad: Optional[SeqPad], kv_valid_len: Optional[int]):
     """Joint attention over ``cat(video, text)`` with the Ulysses exchange.
@@ -213,6 +214,12 @@ class JointAttention(nn.Module):
         tpg = ps.get_tensor_model_parallel_group()
         x = M.copy_to_tensor_model_parallel_region(x, tpg)
         ctx = M.copy_to_tensor_model_parallel_region(ctx, tpg)
+        if ps.get_context_parallel_world_size() == 1:
+            q, k, v = ops.joint_qkv_projection(
+                x, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight, self.k_layernorm.weight,
+                cos, sin, ctx, self.added_linear_qkv.weight, self.added_linear_qkv.bias,
+                self.added_q_layernorm.weight, self.added_k_layernorm.weight, self.heads_local, self.eps)
+            return _joint_attention(q, k, v, ctx.shape[1], kv_valid_len)
         q, k, v = ops.qkv_projection(x, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight,
                                      self.k_layernorm.weight, cos, sin, self.heads_local, self.eps)
         tq, tk, tv = ops.qkv_projection(ctx, self.added_linear_qkv.weight, self.added_linear_qkv.bias,
@@ -238,6 +245,8 @@ class SingleAttention(nn.Module):
         s = h.shape[1] - text_len
         q, k, v = ops.qkv_projection(h, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight,
                                      self.k_layernorm.weight, cos, sin, self.heads_local, self.eps, rope_len=s)
+        if ps.get_context_parallel_world_size() == 1:
+            return _joint_attention(q, k, v, text_len, kv_valid_len)
         return _ulysses_attention(q[:, :, :s], k[:, :, :s], v[:, :, :s], q[:, :, s:], k[:, :, s:], v[:, :, s:],
                                   pad, kv_valid_len)
 
@@ -267,12 +276,13 @@ class HunyuanDiTLayer(nn.Module):
         xn = ops.layernorm_modulate(x, scale_msa, shift_msa, self.eps)
         cn = ops.layernorm_modulate(ctx, c_scale_msa, c_shift_msa, self.eps)
         attn, c_attn = self.self_attention(xn, cn, cos, sin, pad, kv_valid_len)
-        x = self.self_attention.linear_proj.forward_gate_residual(attn, gate_msa, x)
-        ctx = self.self_attention.added_linear_proj.forward_gate_residual(c_attn, c_gate_msa, ctx)
-        xn = ops.layernorm_modulate(x, scale_mlp, shift_mlp, self.eps)
-        cn = ops.layernorm_modulate(ctx, c_scale_mlp, c_shift_mlp, self.eps)
-        x = self.mlp.forward_gate_residual(xn, gate_mlp, x)
-        ctx = self.ff_context.forward_gate_residual(cn, c_gate_mlp, ctx)
+        a = self.self_attention.linear_proj(attn)
+        ca = self.self_attention.added_linear_proj(c_attn)
+        # residual update and the next LayerNorm + modulation in one pass over the tokens
+        x, xn = ops.gate_residual_layernorm_modulate(x, a, gate_msa, scale_mlp, shift_mlp, self.eps)
+        ctx, cn = ops.gate_residual_layernorm_modulate(ctx, ca, c_gate_msa, c_scale_mlp, c_shift_mlp, self.eps)
+        x = ops.gate_residual(x, self.mlp(xn), gate_mlp)
+        ctx = ops.gate_residual(ctx, self.ff_context(cn), c_gate_mlp)
         return x, ctx
 
 
@@ -300,7 +310,7 @@ class HunyuanSingleDiTLayer(nn.Module):
         mlp = self.proj_mlp(hn, activation=self.activation)
         attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len)
         merged = torch.cat([torch.cat([attn, c_attn], dim=1), mlp], dim=2)
-        h = self.proj_out.forward_gate_residual(merged, gate, h)
+        h = ops.gate_residual(h, self.proj_out(merged), gate)
         return h[:, :-T], h[:, -T:]
 
 

@@ -109,13 +109,6 @@ def linear(x, weight, bias=None, activation=None):
     return reference.linear(x, weight, bias, activation)
 
 
-def linear_gate_residual(x, weight, bias, gate, residual):
-    if _use_cuda(x):
-        from . import cuda_ops
-        return cuda_ops.linear_gate_residual(x, weight, bias, gate, residual)
-    return reference.linear_gate_residual(x, weight, bias, gate, residual)
-
-
 def attention(q, k, v, kv_valid_len=None, scale=None):
     if _use_cuda(q):
         from . import cuda_ops
@@ -131,6 +124,18 @@ def qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin, num_
                                        num_heads, eps, rope_len)
     return reference.qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin,
                                     num_heads, eps, rope_len)
+
+
+def joint_qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin, x2, weight2, bias2,
+                         q_norm_weight2, k_norm_weight2, num_heads, eps: float = 1e-6):
+    """Video stream ``x`` (RoPE applied) and text stream ``x2`` (no RoPE), each with its own weights,
+    projected into shared ``[B, heads, S + T, D]`` q / k / v (video tokens first)."""
+    if _use_cuda(x) and q_norm_weight.shape[0] == 128:
+        from . import cuda_ops
+        return cuda_ops.joint_qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin, x2, weight2,
+                                             bias2, q_norm_weight2, k_norm_weight2, num_heads, eps)
+    return reference.joint_qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin, x2, weight2,
+                                          bias2, q_norm_weight2, k_norm_weight2, num_heads, eps)
 
 
 def flow_match_loss(pred, noise, latents, weight):

@@ -1,0 +1,49 @@
+"""Attention entry point of the CUDA op layer.
+
+``attention(q, k, v)`` takes head-major ``[B, h, S, 128]`` bf16 operands (the layout the QKV kernel
+writes) and returns token-major ``[B, S, h * 128]`` (the layout the output projection reads).
+Backend ``tcgen05`` is the hand-written flash attention (``csrc/attn_tcgen05.cu``); backend ``sdpa``
+is the library path (``torch`` SDPA, cuDNN / flash backends), which is what the reference runs
+(``teletron/models/dit/dit_attention.py:313``) and the fallback for shapes the kernel does not take.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+_BACKEND = os.environ.get("TELETRON_B200_ATTN", "auto")
+COUNTERS = {"tcgen05": 0, "sdpa": 0}
+
+
+def set_backend(name: str) -> None:
+    global _BACKEND
+    if name not in ("auto", "tcgen05", "sdpa"):
+        raise ValueError(name)
+    _BACKEND = name
+
+
+def _sdpa(q, k, v, kv_valid_len, scale):
+    COUNTERS["sdpa"] += 1
+    B, h, S, D = q.shape
+    mask = None
+    if kv_valid_len is not None and kv_valid_len < k.shape[2]:
+        mask = torch.zeros(1, 1, 1, k.shape[2], dtype=torch.bool, device=q.device)
+        mask[..., :kv_valid_len] = True
+    o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, scale=scale)
+    return o.transpose(1, 2).reshape(B, S, h * D)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_valid_len: Optional[int] = None,
+              scale: Optional[float] = None) -> torch.Tensor:
+    if _BACKEND != "sdpa":
+        from . import attn_tcgen05
+        if attn_tcgen05.supported(q, k, v):
+            COUNTERS["tcgen05"] += 1
+            return attn_tcgen05.attention(q, k, v, kv_valid_len, scale)
+        if _BACKEND == "tcgen05":
+            raise RuntimeError(f"tcgen05 attention does not take q {tuple(q.shape)}")
+    return _sdpa(q, k, v, kv_valid_len, scale)

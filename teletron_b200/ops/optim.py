@@ -8,13 +8,20 @@ import torch
 
 
 def _pack16(master: torch.Tensor):
-    hi = master.to(torch.bfloat16)
-    lo = (master.view(torch.int32) - (hi.view(torch.int16).to(torch.int32) << 16)).to(torch.int16)
-    return hi, lo
+    """fp32 -> (bf16 weight, int16 remainder).  The weight is the fp32 bit pattern rounded half-up in
+    magnitude to its top 16 bits, so the remainder always lies in [-32768, 32767]."""
+    bits = master.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    hi = ((bits + 0x8000) >> 16) & 0xFFFF
+    lo = bits - (hi << 16)
+    hi16 = torch.where(hi >= 0x8000, hi - 0x10000, hi).to(torch.int16)
+    return hi16.view(torch.bfloat16), lo.to(torch.int16)
 
 
 def _unpack16(hi: torch.Tensor, lo: torch.Tensor) -> torch.Tensor:
-    return ((hi.view(torch.int16).to(torch.int32) << 16) + lo.to(torch.int32)).view(torch.float32)
+    hb = hi.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
+    bits = ((hb << 16) + lo.to(torch.int64)) & 0xFFFFFFFF
+    bits = torch.where(bits >= 0x80000000, bits - 0x100000000, bits).to(torch.int32)
+    return bits.view(torch.float32)
 
 
 def adamw_update_reference(param, grad, exp_avg, exp_avg_sq, master, master_lo, *, lr, beta1, beta2, eps,

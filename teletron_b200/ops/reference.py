@@ -86,11 +86,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return _act(F.linear(x, weight, bias), activation)
 
 
-def linear_gate_residual(x, weight, bias, gate, residual):
-    """``residual + gate[:, None] * (x @ weight.T + bias)``; x is ``[B, S, K]``."""
-    return gate_residual(residual, F.linear(x, weight, bias), gate)
-
-
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               kv_valid_len: Optional[int] = None, scale: Optional[float] = None) -> torch.Tensor:
     """Non-causal softmax attention.
@@ -142,6 +137,13 @@ def qkv_projection(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
             q = torch.cat([apply_rope(q[:, :, :n], cos, sin), q[:, :, n:]], dim=2)
             k = torch.cat([apply_rope(k[:, :, :n], cos, sin), k[:, :, n:]], dim=2)
     return q.contiguous(), k.contiguous(), v
+
+
+def joint_qkv_projection(x, weight, bias, qw, kw, cos, sin, x2, weight2, bias2, qw2, kw2, num_heads, eps=1e-6):
+    """Two streams with separate weights into one concatenated ``[B, h, S + T, D]`` q / k / v."""
+    q, k, v = qkv_projection(x, weight, bias, qw, kw, cos, sin, num_heads, eps)
+    q2, k2, v2 = qkv_projection(x2, weight2, bias2, qw2, kw2, None, None, num_heads, eps)
+    return torch.cat([q, q2], dim=2), torch.cat([k, k2], dim=2), torch.cat([v, v2], dim=2)
 
 
 def flow_match_loss(pred: torch.Tensor, noise: torch.Tensor, latents: torch.Tensor,

@@ -141,7 +141,10 @@ def model_flops_per_sample(num_params_blocks: int, video_tokens: int, text_token
 
 class MetricLogger:
     def __init__(self, jsonl_path: Optional[str] = None, tensorboard_dir: Optional[str] = None, queue_size: int = 10):
-        self.jsonl = open(jsonl_path, "a") if (jsonl_path and is_rank_0()) else None
+        self.jsonl = None
+        if jsonl_path and is_rank_0():
+            os.makedirs(os.path.dirname(os.path.abspath(jsonl_path)), exist_ok=True)
+            self.jsonl = open(jsonl_path, "a")
         self.tb = None
         if tensorboard_dir and is_rank_0():
             try:

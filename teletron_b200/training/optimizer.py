@@ -31,18 +31,7 @@ from ..parallel.grad_buffer import DistributedDataParallel, ParamAndGradBuffer
 from ..parallel import state as ps
 
 
-def split16_pack(master: torch.Tensor):
-    """fp32 -> (bf16 round-to-nearest, int16 remainder) with exact reconstruction."""
-    hi = master.to(torch.bfloat16)
-    bits = master.view(torch.int32)
-    hi_bits = hi.view(torch.int16).to(torch.int32) << 16
-    lo = (bits - hi_bits).to(torch.int16)
-    return hi, lo
-
-
-def split16_unpack(hi: torch.Tensor, lo: torch.Tensor) -> torch.Tensor:
-    bits = (hi.view(torch.int16).to(torch.int32) << 16) + lo.to(torch.int32)
-    return bits.view(torch.float32)
+from ..ops.optim import _pack16 as split16_pack, _unpack16 as split16_unpack  # noqa: E402,F401
 
 
 class _ShardState:
