@@ -237,7 +237,7 @@ def main():
     flops = model_flops_per_sample(cfg.num_parameters(), tokens, a.text_len, cfg.num_attention_heads,
                                    cfg.attention_head_dim, cfg.num_layers + cfg.num_single_layers, not a.no_recompute)
     if rank == 0:
-        from teletron_b200.ops import attention as attn_mod
+        from teletron_b200.ops import attention_backend as attn_mod
         from teletron_b200.ops import gemm as gemm_mod
         out = {"metric": "HunyuanVideo-13B 720P train samples/s", "value": value, "unit": "samples/s",
                "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,

@@ -53,6 +53,10 @@ int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, voi
              int state_is_bf16, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale,
              void* stream);
 
+/* ---- tcgen05 GEMM (see gemm_tcgen05.cu for the layout / epilogue codes) ---- */
+int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
+                 long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

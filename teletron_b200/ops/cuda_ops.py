@@ -335,7 +335,7 @@ def joint_qkv_projection(x, weight, bias, qw, kw, cos, sin, x2, weight2, bias2, 
 # ---------------------------------------------------------------------------------------------
 
 def attention(q, k, v, kv_valid_len=None, scale=None):
-    from . import attention as attn
+    from . import attention_backend as attn
     return attn.attention(q, k, v, kv_valid_len, scale)
 
 
