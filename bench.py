@@ -138,6 +138,9 @@ def main():
     if a.impl == "library":
         # the restated reference path: cuBLAS GEMMs, SDPA attention, unfused PyTorch elementwise ops, NCCL collectives
         ops.set_impl("torch")
+        # the reference turns the cuDNN SDPA backend off and runs PyTorch's flash backend
+        # (teletron/models/dit/dit_attention.py:312)
+        torch.backends.cuda.enable_cudnn_sdp(False)
     tp = a.tp if a.tp is not None else (2 if a.gpus == 8 else 1)
     cp = a.cp if a.cp is not None else max(1, a.gpus // tp)
     single = a.gpus == 1

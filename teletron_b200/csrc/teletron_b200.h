@@ -57,6 +57,10 @@ int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, voi
 int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
 
+/* ---- tcgen05 flash attention forward: q, k, v [B*H, S, 128]; out [B, S, H*128]; lse [B*H, S] ---- */
+int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int kv_len,
+                float scale, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,15 +1,55 @@
-"""Python side of the tcgen05 flash attention (``csrc/attn_tcgen05.cu``)."""
+"""Python side of the tcgen05 flash attention (``csrc/attn_fwd_tcgen05.cu`` / ``csrc/attn_bwd_tcgen05.cu``).
+
+Operands are head-major ``[B, h, S, 128]`` bf16; the result is token-major ``[B, S, h * 128]`` and the
+forward also returns the per-row log-sum-exp ``[B, h, S]`` (fp32, natural log) that the backward uses.
+"""
 
 from __future__ import annotations
+
+import math
+from typing import Optional
 
 import torch
 
 from . import _lib
+from ._lib import c_float, c_int, call, check, ptr, stream
+from .gemm_tcgen05 import status_tensor
+
+BF16 = torch.bfloat16
 
 
 def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
-    return False
+    return (_lib.available() and q.is_cuda and q.dtype == BF16 and q.dim() == 4 and q.shape[-1] == 128
+            and q.shape == k.shape == v.shape)
+
+
+def forward(q, k, v, kv_valid_len: Optional[int], scale: Optional[float]):
+    B, H, S, D = q.shape
+    q, k, v = (check(t.contiguous(), BF16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    out = torch.empty(B, S, H * D, dtype=BF16, device=q.device)
+    lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    kv_len = S if kv_valid_len is None else min(int(kv_valid_len), S)
+    sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    call("tt_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(B), c_int(H), c_int(S), c_int(kv_len),
+         c_float(sc), ptr(status_tensor(q.device)), stream())
+    return out, lse, q, k, v, sc, kv_len
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, kv_valid_len, scale):
+        out, lse, qc, kc, vc, sc, kv_len = forward(q, k, v, kv_valid_len, scale)
+        ctx.save_for_backward(qc, kc, vc, out, lse)
+        ctx.sc, ctx.kv_len = sc, kv_len
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from . import attn_backward
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attn_backward.backward(dout.contiguous(), q, k, v, out, lse, ctx.sc, ctx.kv_len)
+        return dq, dk, dv, None, None
 
 
 def attention(q, k, v, kv_valid_len=None, scale=None):
-    raise _lib.NativeError("tcgen05 attention is not built")
+    return _Attention.apply(q, k, v, kv_valid_len, scale)

@@ -1,0 +1,71 @@
+"""tcgen05 flash attention against an fp32 PyTorch softmax attention."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+def _ref(q, k, v, kv_len=None, scale=None):
+    qf, kf, vf = q.float(), k.float(), v.float()
+    s = qf @ kf.transpose(-1, -2) * (scale or 1.0 / math.sqrt(q.shape[-1]))
+    if kv_len is not None:
+        s[..., kv_len:] = float("-inf")
+    p = s.softmax(-1)
+    o = p @ vf
+    B, H, S, D = q.shape
+    return o.transpose(1, 2).reshape(B, S, H * D), torch.logsumexp(s, -1)
+
+
+@pytest.mark.parametrize("B,H,S,kv_len", [(1, 2, 256, None), (1, 3, 1000, None), (2, 2, 513, None), (1, 2, 900, 777),
+                                          (1, 1, 128, None), (1, 2, 3000, None), (1, 1, 200, 130)])
+def test_forward(B, H, S, kv_len):
+    from teletron_b200.ops import attn_tcgen05 as A
+    from teletron_b200.ops.gemm_tcgen05 import check_status
+    g = torch.Generator(device="cuda").manual_seed(S + H)
+    q, k, v = ((torch.randn(B, H, S, 128, device="cuda", generator=g) * s).bfloat16() for s in (1.0, 1.0, 1.0))
+    out, lse, *_ = A.forward(q, k, v, kv_len, None)
+    check_status()
+    ro, rl = _ref(q, k, v, kv_len)
+    assert _rel(out, ro) < 1.2e-2, _rel(out, ro)
+    torch.testing.assert_close(lse, rl, rtol=2e-3, atol=2e-3)
+
+
+def test_forward_large_scores_trigger_rescale():
+    """Keys ordered by growing norm so the row maximum keeps rising across KV tiles."""
+    from teletron_b200.ops import attn_tcgen05 as A
+    from teletron_b200.ops.gemm_tcgen05 import check_status
+    g = torch.Generator(device="cuda").manual_seed(0)
+    S = 1024
+    q = (torch.randn(1, 2, S, 128, device="cuda", generator=g) * 2).bfloat16()
+    ramp = torch.linspace(0.2, 6.0, S, device="cuda").view(1, 1, S, 1)
+    k = (torch.randn(1, 2, S, 128, device="cuda", generator=g) * ramp).bfloat16()
+    v = torch.randn(1, 2, S, 128, device="cuda", generator=g).bfloat16()
+    out, lse, *_ = A.forward(q, k, v, None, None)
+    check_status()
+    ro, rl = _ref(q, k, v)
+    assert _rel(out, ro) < 1.5e-2
+    torch.testing.assert_close(lse, rl, rtol=2e-3, atol=5e-3)
+
+
+@pytest.mark.parametrize("S,kv_len", [(640, None), (300, 260)])
+def test_autograd_matches_reference(S, kv_len):
+    from teletron_b200.ops import attn_tcgen05 as A
+    from teletron_b200.ops import reference
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q, k, v = (torch.randn(1, 2, S, 128, device="cuda", generator=g).bfloat16().requires_grad_() for _ in range(3))
+    d = torch.randn(1, S, 256, device="cuda", generator=g).bfloat16()
+    o = A.attention(q, k, v, kv_len, None)
+    o.backward(d)
+    refs = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ro = reference.attention(*refs, kv_len, None)
+    ro.backward(d.float())
+    assert _rel(o, ro) < 1.2e-2
+    for a, r in zip((q, k, v), refs):
+        assert _rel(a.grad, r.grad) < 2e-2

@@ -196,11 +196,13 @@ def test_block_cuda_matches_torch():
             pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"), device=dev, dtype=torch.bfloat16)
             loss = pipe(batch)[0]
             loss.backward()
-            out[impl] = (float(loss), {n: p.grad.float().clone() for n, p in pipe.transformer.named_parameters()
+            out[impl] = (float(loss.detach()), {n: p.grad.float().clone() for n, p in pipe.transformer.named_parameters()
                                       if p.grad is not None})
     assert abs(out["cuda"][0] - out["torch"][0]) < 2e-2 * abs(out["torch"][0])
     bad = []
     for n, gt in out["torch"][1].items():
+        if n.endswith("to_k.bias"):
+            continue        # softmax is invariant to a shift of all keys: this gradient is pure rounding noise
         r = _rel(out["cuda"][1][n], gt)
         if r > 0.08:
             bad.append((n, r))
