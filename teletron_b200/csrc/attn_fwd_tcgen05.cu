@@ -33,6 +33,12 @@ constexpr int kTileBytes = 2 * kSlab;   // a [128 x 128] bf16 tile = two slabs (
 constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 struct AttnParams {
     __nv_bfloat16* out;   // [B, S, H*128]
     float* lse;           // [B*H, S]
@@ -188,20 +194,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!mbar_wait(s_full(t), (uint32_t)j & 1u, &abort_flag)) goto done;
             tc_fence_after();
             const int valid = p.kv_len - j * BKV;      // columns >= valid are masked (only in the last tile)
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
+            const bool full_tile = valid >= BKV;
+            // pass 1: row maximum (3-input max, four independent chains)
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
             for (int c = 0; c < BKV / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32(tS + c * 32, r);
                 tmem_ld_wait();
+                if (!full_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float sv = (c * 32 + i < valid) ? __uint_as_float(r[i]) : -INFINITY;
-                    mx = fmaxf(mx, sv);
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i >= valid) r[i] = 0xff800000u;      // -inf
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                    mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    mx2 = max3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                    mx3 = max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
                 }
             }
-            mx *= p.scale_log2;
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             // lazy rescale of the accumulator
             const bool grow = mx > m + kRescaleThreshold || j == 0;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -219,9 +233,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 tmem_st_wait();
             }
             if (grow) m = mx;
-            // pass 2: P = exp2(s * scale - m), row sum, bf16 pack, store over S
-            float sum = 0.f;
-#pragma unroll 1
+            // pass 2: P = exp2(s * scale - m) with packed fp32x2 arithmetic, row sum, bf16 pack, store over S
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            const float2 nm2 = make_float2(-m, -m);
+            float2 sum2a = make_float2(0.f, 0.f), sum2b = make_float2(0.f, 0.f);
+#pragma unroll
             for (int c = 0; c < BKV / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32(tS + c * 32, r);
@@ -229,17 +245,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const int c0 = c * 32 + 2 * i;
-                    const float e0 = (c0 < valid) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m) : 0.f;
-                    const float e1 = (c0 + 1 < valid) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m) : 0.f;
-                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    // the sum uses the rounded values so that O / l is an exact convex combination
-                    const float2 back = __bfloat1622float2(b2);
-                    sum += back.x + back.y;
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, nm2);
+                    float2 e = make_float2(exp2f(x.x), exp2f(x.y));
+                    if (!full_tile) {
+                        const int c0 = c * 32 + 2 * i;
+                        if (c0 >= valid) e.x = 0.f;
+                        if (c0 + 1 >= valid) e.y = 0.f;
+                    }
+                    if (i & 1) sum2b = __fadd2_rn(sum2b, e);
+                    else sum2a = __fadd2_rn(sum2a, e);
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(e.x, e.y);
                     pk[i] = *reinterpret_cast<const uint32_t*>(&b2);
                 }
                 tmem_st_32x16(tS + c * 16, pk);
             }
+            const float sum = (sum2a.x + sum2a.y) + (sum2b.x + sum2b.y);
             l += sum;
             tmem_st_wait();
             tc_fence_before();
