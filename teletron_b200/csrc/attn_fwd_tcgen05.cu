@@ -41,7 +41,8 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 struct AttnParams {
     __nv_bfloat16* out;   // [B, S, H*128]
-    float* lse;           // [B*H, S]
+    float* lse;           // [B*H, lse_pitch]
+    int lse_pitch;
     int S;                // query / key sequence length
     int kv_len;           // keys >= kv_len are masked
     int H;                // heads (for the output layout)
@@ -287,7 +288,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             }
         }
-        if (row < p.S) p.lse[(long)bh * p.S + row] = (m + log2f(l)) * 0.6931471805599453f;
+        if (row < p.S) p.lse[(long)bh * p.lse_pitch + row] = (m + log2f(l)) * 0.6931471805599453f;
     }
 
 done:
@@ -305,10 +306,10 @@ done:
 
 }  // namespace
 
-// q, k, v: [BH, S, 128] bf16 contiguous; out [B, S, H*128] bf16; lse [BH, S] fp32.
+// q, k, v: [BH, S, 128] bf16 contiguous; out [B, S, H*128] bf16; lse [BH, lse_pitch] fp32 (rows < S written).
 extern "C" int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
-                           int kv_len, float scale, int* status, void* stream) {
-    if (B <= 0 || H <= 0 || S <= 0 || kv_len <= 0 || kv_len > S || status == nullptr) return TT_ERR_ARG;
+                           int kv_len, int lse_pitch, float scale, int* status, void* stream) {
+    if (B <= 0 || H <= 0 || S <= 0 || kv_len <= 0 || kv_len > S || lse_pitch < S || status == nullptr) return TT_ERR_ARG;
     CUtensorMap tq, tk, tv;
     int rc;
     const uint64_t BH = (uint64_t)B * H;
@@ -324,6 +325,7 @@ extern "C" int tt_attn_fwd(const void* q, const void* k, const void* v, void* ou
     AttnParams p;
     p.out = (__nv_bfloat16*)out;
     p.lse = lse;
+    p.lse_pitch = lse_pitch;
     p.S = S;
     p.kv_len = kv_len;
     p.H = H;

@@ -337,6 +337,20 @@ int tt_make_tmap_3d(CUtensorMap* out, const void* base, uint64_t d2, uint64_t d1
     return r == CUDA_SUCCESS ? TT_OK : TT_ERR_ARG;
 }
 
+int tt_make_tmap_bshd(CUtensorMap* out, const void* base, uint64_t B, uint64_t S, uint64_t H, uint32_t box_rows) {
+    tt_encode_tiled_fn enc = tt_get_encode_tiled();
+    if (enc == nullptr) return TT_ERR_CUDA;
+    if (((uintptr_t)base & 15) || box_rows > 256) return TT_ERR_ARG;
+    cuuint64_t dims[4] = {128, H, S, B};
+    cuuint64_t strides[3] = {128 * 2, H * 128 * 2, S * H * 128 * 2};
+    cuuint32_t box[4] = {64, 1, box_rows, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TT_OK : TT_ERR_ARG;
+}
+
 // C[M, N] = epilogue(op(A) op(B)^T ...) as described at the top of this file.
 //   a_mn == 0: a is A[M, K] with row pitch lda;   a_mn == 1: a is A^T stored [K, M] with row pitch lda
 //   b_mn == 0: b is B[N, K] with row pitch ldb;   b_mn == 1: b is B stored [K, N] with row pitch ldb

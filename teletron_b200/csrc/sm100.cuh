@@ -75,6 +75,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
         "l"((uint64_t)tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* tmap, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+            smem_dst),
+        "l"((uint64_t)tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tmap) : "memory");
 }
@@ -191,3 +199,5 @@ int tt_make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 // 3-D bf16 tensor [d2, d1, d0] (d0 contiguous), box [1, box1, box0], 128B swizzle.
 int tt_make_tmap_3d(CUtensorMap* out, const void* base, uint64_t d2, uint64_t d1, uint64_t d0, uint64_t stride1,
                     uint64_t stride2, uint32_t box1, uint32_t box0);
+// Token-major activations [B, S, H, 128] viewed per head: coordinates (col, head, row, batch), box [1, box_rows, 1, 64].
+int tt_make_tmap_bshd(CUtensorMap* out, const void* base, uint64_t B, uint64_t S, uint64_t H, uint32_t box_rows);

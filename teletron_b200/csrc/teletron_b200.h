@@ -10,6 +10,9 @@
 extern "C" {
 #endif
 
+#include <stddef.h>
+
+#define TT_MAX_PEERS 8
 #define TT_NORM_MAX_PARTIAL_BLOCKS 1024
 #define TT_QKV_MAX_PARTIAL_WARPS 4736
 
@@ -57,9 +60,27 @@ int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, voi
 int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
 
-/* ---- tcgen05 flash attention forward: q, k, v [B*H, S, 128]; out [B, S, H*128]; lse [B*H, S] ---- */
+/* ---- tcgen05 flash attention: q, k, v, dq, dk, dv [B*H, S, 128]; out, dout [B, S, H*128];
+ *      lse, delta [B*H, pitch] fp32, pitch % 64 == 0, lse = +inf and delta = 0 at positions >= S ---- */
 int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int kv_len,
-                float scale, int* status, void* stream);
+                int lse_pitch, float scale, int* status, void* stream);
+int tt_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len, int pitch, float scale,
+                int* status, void* stream);
+
+/* ---- symmetric heap + in-kernel collectives over IPC-mapped peer memory (comm.cu) ---- */
+int tt_symm_alloc(size_t bytes, void** out);                 /* cudaMalloc + zero */
+int tt_symm_free(void* p);
+int tt_ipc_get_handle(void* p, void* handle64);              /* 64-byte CUDA IPC handle */
+int tt_ipc_open(const void* handle64, void** out);
+int tt_ipc_close(void* p);
+/* flag_ptrs[r] = rank r's array of n 64-bit flags (peer-mapped); sets TT_ERR_TIMEOUT in *status on expiry */
+int tt_comm_barrier(void* const* flag_ptrs, int my_rank, int n, unsigned long long epoch, long long timeout_cycles,
+                    int* status, void* stream);
+int tt_reduce_scatter_bf16(void* const* src_ptrs, int n, long offset, void* out, long count, float scale, void* stream);
+int tt_all_gather_push_bf16(void* const* dst_ptrs, int n, long offset, const void* src, long count, void* stream);
+int tt_partial_sum(const void* stage, int n, long rows, int cols, const void* bias, const void* res, const void* gate,
+                   long rows_per_batch, void* out, void* stream);
 
 #ifdef __cplusplus
 }

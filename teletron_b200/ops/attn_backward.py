@@ -21,7 +21,7 @@ def _flash(dout, q, k, v, out, lse, scale):
     B, H, S, D = q.shape
     dq, dk, dv = (torch.empty(B, H, S, D, dtype=q.dtype, device=q.device) for _ in range(3))
     _flash_attn_backward(dout.view(B, S, H, D), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                         out.view(B, S, H, D), lse, dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2),
+                         out.view(B, S, H, D), lse[..., :S].contiguous(), dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2),
                          0.0, scale, False, -1, -1, 0.0, None, False, None)
     return dq, dk, dv
 

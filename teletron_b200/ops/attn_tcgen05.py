@@ -1,7 +1,8 @@
 """Python side of the tcgen05 flash attention (``csrc/attn_fwd_tcgen05.cu`` / ``csrc/attn_bwd_tcgen05.cu``).
 
 Operands are head-major ``[B, h, S, 128]`` bf16; the result is token-major ``[B, S, h * 128]`` and the
-forward also returns the per-row log-sum-exp ``[B, h, S]`` (fp32, natural log) that the backward uses.
+forward also returns the per-row log-sum-exp (fp32, natural log; ``[B, h, pitch]`` with ``pitch`` = S rounded up
+to 64 and ``+inf`` in the padding) that the backward uses.
 """
 
 from __future__ import annotations
@@ -27,11 +28,12 @@ def forward(q, k, v, kv_valid_len: Optional[int], scale: Optional[float]):
     B, H, S, D = q.shape
     q, k, v = (check(t.contiguous(), BF16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
     out = torch.empty(B, S, H * D, dtype=BF16, device=q.device)
-    lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    pitch = (S + 63) // 64 * 64       # the backward reads statistics in aligned chunks of 64 queries
+    lse = torch.full((B, H, pitch), float("inf"), dtype=torch.float32, device=q.device)
     kv_len = S if kv_valid_len is None else min(int(kv_valid_len), S)
     sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
     call("tt_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(B), c_int(H), c_int(S), c_int(kv_len),
-         c_float(sc), ptr(status_tensor(q.device)), stream())
+         c_int(pitch), c_float(sc), ptr(status_tensor(q.device)), stream())
     return out, lse, q, k, v, sc, kv_len
 
 

@@ -34,7 +34,7 @@ def test_forward(B, H, S, kv_len):
     check_status()
     ro, rl = _ref(q, k, v, kv_len)
     assert _rel(out, ro) < 1.2e-2, _rel(out, ro)
-    torch.testing.assert_close(lse, rl, rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(lse[..., :S], rl, rtol=2e-3, atol=2e-3)
 
 
 def test_forward_large_scores_trigger_rescale():
@@ -51,10 +51,10 @@ def test_forward_large_scores_trigger_rescale():
     check_status()
     ro, rl = _ref(q, k, v)
     assert _rel(out, ro) < 1.5e-2
-    torch.testing.assert_close(lse, rl, rtol=2e-3, atol=5e-3)
+    torch.testing.assert_close(lse[..., :S], rl, rtol=2e-3, atol=5e-3)
 
 
-@pytest.mark.parametrize("S,kv_len", [(640, None), (300, 260)])
+@pytest.mark.parametrize("S,kv_len", [(640, None), (300, 260), (128, None), (1000, None), (2100, 2000)])
 def test_autograd_matches_reference(S, kv_len):
     from teletron_b200.ops import attn_tcgen05 as A
     from teletron_b200.ops import reference
