@@ -20,6 +20,8 @@
 #include "sm100.cuh"
 #include "teletron_b200.h"
 
+#include <string.h>
+
 namespace {
 
 using namespace sm100;
@@ -29,14 +31,42 @@ constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;
 
+struct TmapArray {
+    CUtensorMap m[TT_MAX_PEERS];
+};
+
 struct GemmParams {
     int M, N, K;
     __nv_bfloat16* C;
     long ldc;
     const __nv_bfloat16* bias;
-    __nv_bfloat16* aux;     // EPI 1/2: pre-activation output; EPI 3/4: pre-activation input
+    __nv_bfloat16* aux;     // EPI 1/2: pre-activation output; EPI 3/4: pre-activation input; EPI 5: raw QKV output
     int* status;
     int tiles_m, tiles_n;
+    // ---- operand A gathered from several ranks (tensor maps over peer memory, plain non-multicast TMA) ----
+    int a_mode;             // 0: one source; 1: source chosen by K column block (head -> owner rank);
+                            // 2: source chosen by M segment (all-gather of row blocks)
+    int a_span;             // mode 1: K columns held by each source
+    int a_row_off;          // mode 0/1: row offset of this rank's rows inside the source tensor
+    int n_seg, seg_rows;    // M is n_seg segments of seg_rows rows (n_seg == 1: plain)
+    int seg_rot;            // first segment processed (own rank's rows first)
+    int my_rank;
+    // ---- where the output tile goes ----
+    int store_mode;         // 0: C (local); 1: column block -> peer_out[col / out_span] (head -> owner);
+                            // 2: row segment -> peer_out[segment] staging slot of this rank (reduce-scatter push)
+    int out_span, out_row_off;
+    long out_ld;
+    __nv_bfloat16* peer_out[TT_MAX_PEERS];
+    // ---- fused QKV epilogue (EPI 5): bias, QK-RMSNorm, RoPE, head-major scatter to the head's owner rank ----
+    const __nv_bfloat16* qw;
+    const __nv_bfloat16* kw;
+    const float* cos_t;
+    const float* sin_t;
+    float eps;
+    int rope_len, heads_per_rank, s_in, s_out, out_off, only_local;
+    __nv_bfloat16* peer_q[TT_MAX_PEERS];
+    __nv_bfloat16* peer_k[TT_MAX_PEERS];
+    __nv_bfloat16* peer_v[TT_MAX_PEERS];
 };
 
 template <int BN>
@@ -60,7 +90,7 @@ __device__ __forceinline__ float epi_apply(float acc, float b, float u) {
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int abort_flag;
@@ -87,7 +117,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         fence_barrier_init();
         fence_proxy_async();
-        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmA.m[0]);
         tma_prefetch_desc(&tmB);
     }
     if (warp == 1) {
@@ -101,13 +131,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int kblocks = (p.K + BK - 1) / BK;
-    auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int tiles_per_seg = p.tiles_m / p.n_seg;
+    // tile index -> (segment, first row inside the segment, first column)
+    auto tile_coords = [&](int t, int& seg, int& m0, int& n0) {
         const int per_group = kGroupM * p.tiles_n;
         const int g = t / per_group;
         const int first_m = g * kGroupM;
         const int gm = min(kGroupM, p.tiles_m - first_m);
         const int r = t - g * per_group;
-        m0 = (first_m + r % gm) * BM;
+        const int mt = first_m + r % gm;
+        const int si = mt / tiles_per_seg;
+        seg = si + p.seg_rot;
+        if (seg >= p.n_seg) seg -= p.n_seg;
+        m0 = (mt - si * tiles_per_seg) * BM;
         n0 = (r / gm) * BN;
     };
 
@@ -117,8 +153,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             int stage = 0;
             uint32_t phase = 0;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-                int m0, n0;
-                tile_coords(t, m0, n0);
+                int seg, m0, n0;
+                tile_coords(t, seg, m0, n0);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag)) goto done;
                     const uint32_t sa = base + stage * C::kStageBytes;
@@ -126,10 +162,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     mbar_arrive_expect_tx(full_bar(stage), C::kStageBytes);
                     const int k0 = kb * BK;
                     if (!A_MN) {
-                        tma_load_2d(sa, &tmA, full_bar(stage), k0, m0);
+                        // pick the source tensor: local, the owner of this K block (head), or the owner of this row segment
+                        const CUtensorMap* ta = &tmA.m[0];
+                        int ak = k0, am = p.a_row_off + seg * p.seg_rows + m0;
+                        if (p.a_mode == 1) {
+                            const int src = k0 / p.a_span;
+                            ta = &tmA.m[src];
+                            ak = k0 - src * p.a_span;
+                        } else if (p.a_mode == 2) {
+                            ta = &tmA.m[seg];
+                            am = m0;
+                        }
+                        tma_load_2d(sa, ta, full_bar(stage), ak, am);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, full_bar(stage), m0 + 64 * j, k0);
+                        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA.m[0], full_bar(stage), m0 + 64 * j, k0);
                     }
                     if (!B_MN) {
                         tma_load_2d(sb, &tmB, full_bar(stage), k0, n0);
@@ -184,40 +231,115 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int quad = warp & 3;
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
-            int m0, n0;
-            tile_coords(t, m0, n0);
+            int seg, m0, n0;
+            tile_coords(t, seg, m0, n0);
             const int buf = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             if (!mbar_wait(tfull_bar(buf), acc_phase, &abort_flag)) goto done;
             tc_fence_after();
-            const int row = m0 + quad * 32 + lane;
-            const bool row_ok = row < p.M;
-            __nv_bfloat16* crow = p.C + (long)row * p.ldc;
-            __nv_bfloat16* arow = (EPI != 0) ? p.aux + (long)row * p.ldc : nullptr;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
-                tmem_ld_wait();
-                const int col0 = n0 + c * 32;
+            const int lrow = m0 + quad * 32 + lane;                 // row inside the segment
+            const int row = seg * p.seg_rows + lrow;                // row of the logical output
+            const bool row_ok = lrow < p.seg_rows && row < p.M;
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+            if (EPI == 5) {
+                // ---- fused QKV epilogue: this 128-column tile is one head's q, k or v ----
+                const int idx = n0 / 128;
+                const int head = idx / 3, which = idx - head * 3;
+                const int dest = head / p.heads_per_rank, hl = head - dest * p.heads_per_rank;
+                float v[128];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int col = col0 + g * 8;
-                    if (row_ok && col + 8 <= p.N) {
-                        float bv[8], uv[8], o[8];
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tacc + c * 32, r);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) bv[j] = uv[j] = 0.f;
-                        if (EPI <= 2 && p.bias != nullptr) tt::unpack8(tt::ld8(p.bias + col), bv);
-                        if (EPI >= 3) tt::unpack8(tt::ld8(arow + col), uv);
+                    for (int g = 0; g < 4; ++g) {
+                        float bv[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) o[j] = epi_apply<EPI>(__uint_as_float(r[g * 8 + j]), bv[j], uv[j]);
-                        if (EPI == 1 || EPI == 2) {
-                            float u[8];
+                        for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+                        if (p.bias != nullptr) tt::unpack8(tt::ld8(p.bias + n0 + c * 32 + g * 8), bv);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) u[j] = __uint_as_float(r[g * 8 + j]) + bv[j];
-                            tt::st8(arow + col, tt::pack8(u));
+                        for (int j = 0; j < 8; ++j) v[c * 32 + g * 8 + j] = __uint_as_float(r[g * 8 + j]) + bv[j];
+                    }
+                }
+                if (row_ok && (!p.only_local || dest == p.my_rank)) {
+                    if (p.aux != nullptr) {
+                        __nv_bfloat16* arow = p.aux + (long)row * p.ldc + n0;
+#pragma unroll
+                        for (int g = 0; g < 16; ++g) tt::st8(arow + g * 8, tt::pack8(v + g * 8));
+                    }
+                    const int b = row / p.s_in, srow = row - b * p.s_in;
+                    if (which < 2) {
+                        float ss = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 128; ++j) ss += v[j] * v[j];
+                        const float rstd = rsqrtf(ss * (1.f / 128.f) + p.eps);
+                        const __nv_bfloat16* w = which == 0 ? p.qw : p.kw;
+#pragma unroll
+                        for (int g = 0; g < 16; ++g) {
+                            float wv[8];
+                            tt::unpack8(tt::ld8(w + g * 8), wv);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[g * 8 + j] *= rstd * wv[j];
                         }
-                        tt::st8(crow + col, tt::pack8(o));
+                        if (srow < p.rope_len) {
+                            const float4* c4 = reinterpret_cast<const float4*>(p.cos_t + (long)srow * 128);
+                            const float4* s4 = reinterpret_cast<const float4*>(p.sin_t + (long)srow * 128);
+#pragma unroll
+                            for (int g = 0; g < 32; ++g) {
+                                const float4 cc = c4[g], sn = s4[g];
+                                const float a0 = v[4 * g], a1 = v[4 * g + 1], a2 = v[4 * g + 2], a3 = v[4 * g + 3];
+                                v[4 * g] = a0 * cc.x - a1 * sn.x;
+                                v[4 * g + 1] = a1 * cc.y + a0 * sn.y;
+                                v[4 * g + 2] = a2 * cc.z - a3 * sn.z;
+                                v[4 * g + 3] = a3 * cc.w + a2 * sn.w;
+                            }
+                        }
+                    }
+                    __nv_bfloat16* dbase = which == 0 ? p.peer_q[dest] : (which == 1 ? p.peer_k[dest] : p.peer_v[dest]);
+                    __nv_bfloat16* drow = dbase + (((long)b * p.heads_per_rank + hl) * p.s_out + p.out_off + srow) * 128;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) tt::st8(drow + g * 8, tt::pack8(v + g * 8));
+                }
+            } else {
+                // where this tile's rows land: local C, the owner rank of a column block, or an owner's staging slot
+                __nv_bfloat16* crow;
+                int ccol = n0;
+                if (p.store_mode == 0) {
+                    crow = p.C + (long)row * p.ldc;
+                } else if (p.store_mode == 1) {
+                    const int dest = n0 / p.out_span;
+                    ccol = n0 - dest * p.out_span;
+                    crow = p.peer_out[dest] + (long)(p.out_row_off + row) * p.out_ld;
+                } else {
+                    crow = p.peer_out[seg] + ((long)p.my_rank * p.seg_rows + lrow) * p.out_ld;
+                }
+                __nv_bfloat16* arow = (EPI != 0) ? p.aux + (long)row * p.ldc : nullptr;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tacc + c * 32, r);
+                    tmem_ld_wait();
+                    const int col0 = n0 + c * 32;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int col = col0 + g * 8;
+                        if (row_ok && col + 8 <= p.N) {
+                            float bv[8], uv[8], o[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) bv[j] = uv[j] = 0.f;
+                            if (EPI <= 2 && p.bias != nullptr) tt::unpack8(tt::ld8(p.bias + col), bv);
+                            if (EPI >= 3) tt::unpack8(tt::ld8(arow + col), uv);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) o[j] = epi_apply<EPI>(__uint_as_float(r[g * 8 + j]), bv[j], uv[j]);
+                            if (EPI == 1 || EPI == 2) {
+                                float u[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) u[j] = __uint_as_float(r[g * 8 + j]) + bv[j];
+                                tt::st8(arow + col, tt::pack8(u));
+                            }
+                            tt::st8(crow + ccol + (col - n0), tt::pack8(o));
+                        }
                     }
                 }
             }
@@ -242,7 +364,7 @@ done:
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t st) {
+int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t st) {
     using C = Cfg<BN>;
     auto kern = gemm_kernel<BN, A_MN, B_MN, EPI>;
     static bool configured = false;
@@ -259,12 +381,13 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, 
 }
 
 template <int BN>
-int dispatch(bool a_mn, bool b_mn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms,
+int dispatch(bool a_mn, bool b_mn, int epi, const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms,
              cudaStream_t st) {
     if (!a_mn && !b_mn) {
         if (epi == 0) return launch<BN, false, false, 0>(tmA, tmB, p, sms, st);
         if (epi == 1) return launch<BN, false, false, 1>(tmA, tmB, p, sms, st);
         if (epi == 2) return launch<BN, false, false, 2>(tmA, tmB, p, sms, st);
+        if (epi == 5 && BN == 128) return launch<128, false, false, 5>(tmA, tmB, p, sms, st);
     } else if (!a_mn && b_mn) {
         if (epi == 0) return launch<BN, false, true, 0>(tmA, tmB, p, sms, st);
         if (epi == 3) return launch<BN, false, true, 3>(tmA, tmB, p, sms, st);
@@ -351,6 +474,21 @@ int tt_make_tmap_bshd(CUtensorMap* out, const void* base, uint64_t B, uint64_t S
     return r == CUDA_SUCCESS ? TT_OK : TT_ERR_ARG;
 }
 
+namespace {
+
+void default_params(GemmParams& p) {
+    memset(&p, 0, sizeof(p));
+    p.n_seg = 1;
+}
+
+int pick_bn(int M, int N, int sms, bool force128) {
+    // 128 x 256 tiles unless they would leave most SMs idle or N is not a multiple of 256 but is of 128
+    const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    return (force128 || (N % 256 != 0 && N % 128 == 0) || tiles256 < sms) ? 128 : 256;
+}
+
+}  // namespace
+
 // C[M, N] = epilogue(op(A) op(B)^T ...) as described at the top of this file.
 //   a_mn == 0: a is A[M, K] with row pitch lda;   a_mn == 1: a is A^T stored [K, M] with row pitch lda
 //   b_mn == 0: b is B[N, K] with row pitch ldb;   b_mn == 1: b is B stored [K, N] with row pitch ldb
@@ -361,31 +499,147 @@ extern "C" int tt_gemm_bf16(const void* a, const void* b, void* c, const void* b
                             long lda, long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7) || (ldc & 7) || status == nullptr) return TT_ERR_ARG;
     if (a_mn && (M & 7)) return TT_ERR_ARG;
-    if (epi != 0 && aux == nullptr) return TT_ERR_ARG;
+    if (epi < 0 || epi > 4 || (epi != 0 && aux == nullptr)) return TT_ERR_ARG;
     if (((uintptr_t)c & 15) || (bias && ((uintptr_t)bias & 15)) || (aux && ((uintptr_t)aux & 15))) return TT_ERR_ARG;
     const int sms = sm_count();
-    // 128 x 256 tiles unless they would leave most SMs idle or N is not a multiple of 256 but is of 128
-    const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
-    const bool use128 = (N % 256 != 0 && N % 128 == 0) || tiles256 < sms;
-    const int BN = use128 ? 128 : 256;
-    CUtensorMap tmA, tmB;
+    const int BN = pick_bn(M, N, sms, false);
+    TmapArray tmA;
+    CUtensorMap tmB;
     int rc;
-    if (!a_mn) rc = tt_make_tmap_2d(&tmA, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
-    else rc = tt_make_tmap_2d(&tmA, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64);
+    if (!a_mn) rc = tt_make_tmap_2d(&tmA.m[0], a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK);
+    else rc = tt_make_tmap_2d(&tmA.m[0], a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64);
     if (rc != TT_OK) return rc;
     if (!b_mn) rc = tt_make_tmap_2d(&tmB, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, BK);
     else rc = tt_make_tmap_2d(&tmB, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
     if (rc != TT_OK) return rc;
     GemmParams p;
+    default_params(p);
     p.M = M; p.N = N; p.K = K;
     p.C = (__nv_bfloat16*)c;
     p.ldc = ldc;
     p.bias = (const __nv_bfloat16*)bias;
     p.aux = (__nv_bfloat16*)aux;
     p.status = status;
+    p.seg_rows = M;
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + BN - 1) / BN;
     cudaStream_t st = (cudaStream_t)stream;
-    return use128 ? dispatch<128>(a_mn != 0, b_mn != 0, epi, tmA, tmB, p, sms, st)
-                  : dispatch<256>(a_mn != 0, b_mn != 0, epi, tmA, tmB, p, sms, st);
+    return BN == 128 ? dispatch<128>(a_mn != 0, b_mn != 0, epi, tmA, tmB, p, sms, st)
+                     : dispatch<256>(a_mn != 0, b_mn != 0, epi, tmA, tmB, p, sms, st);
+}
+
+// GEMM fused with a collective over peer memory (n ranks of one NVLink domain).  A is K-major.
+//   a_mode 0: a_ptrs[0] is A[a_rows, K] (local), this rank's rows start at a_row_off.
+//   a_mode 1: head -> sequence all-to-all fused into the operand fetch: a_ptrs[r] is rank r's
+//             [a_rows, a_span] tensor holding K columns [r*a_span, (r+1)*a_span) for all rows; this rank's M rows
+//             start at a_row_off in each of them (K == n * a_span).
+//   a_mode 2: all-gather fused into the operand fetch: a_ptrs[r] is rank r's [seg_rows, K] row block; M == n * seg_rows.
+//   b is B[N, K] (b_mn 0) or [K, N] (b_mn 1), always local.
+//   store_mode 0: C local.  1: column block j of width out_span goes to out_ptrs[j] (token rows out_row_off + row,
+//             row pitch out_ld): the sequence -> head all-to-all of a data gradient.  2: row segment i goes to
+//             out_ptrs[i] + my_rank * seg_rows * N: partial sums pushed to their owner (reduce-scatter; sum with
+//             tt_partial_sum after a barrier).
+extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off,
+                                 const void* b, int b_mn, long ldb, void* c, long ldc, const void* bias, int M, int N,
+                                 int K, int seg_rows, int my_rank, int store_mode, void* const* out_ptrs, int out_span,
+                                 int out_row_off, long out_ld, int* status, void* stream) {
+    if (n < 1 || n > TT_MAX_PEERS || M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7) || status == nullptr) return TT_ERR_ARG;
+    if (a_mode < 0 || a_mode > 2 || store_mode < 0 || store_mode > 2 || my_rank < 0 || my_rank >= n) return TT_ERR_ARG;
+    if (a_mode == 1 && ((a_span % BK) || (long)a_span * n != K)) return TT_ERR_ARG;
+    const bool segmented = a_mode == 2 || store_mode == 2;
+    if (segmented && (seg_rows <= 0 || (long)seg_rows * n != M)) return TT_ERR_ARG;
+    if (store_mode == 0 && (c == nullptr || (ldc & 7))) return TT_ERR_ARG;
+    if (store_mode != 0 && (out_ptrs == nullptr || (out_ld & 7))) return TT_ERR_ARG;
+    if (store_mode == 1 && (out_span <= 0 || (out_span % 128) || N % out_span)) return TT_ERR_ARG;
+    const int sms = sm_count();
+    // a column block routed to one peer must not straddle two tiles' owners: 128-wide tiles when spans are 128-multiples
+    const int BN = pick_bn(M, N, sms, store_mode == 1 && (out_span % 256) != 0);
+    TmapArray tmA;
+    CUtensorMap tmB;
+    int rc;
+    const int n_src = a_mode == 0 ? 1 : n;
+    for (int r = 0; r < n_src; ++r) {
+        const uint64_t rows = a_mode == 2 ? (uint64_t)seg_rows : (uint64_t)a_rows;
+        const uint64_t cols = a_mode == 1 ? (uint64_t)a_span : (uint64_t)K;
+        if ((rc = tt_make_tmap_2d(&tmA.m[r], a_ptrs[r], rows, cols, cols, BM, BK)) != TT_OK) return rc;
+    }
+    if (!b_mn) rc = tt_make_tmap_2d(&tmB, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, BK);
+    else rc = tt_make_tmap_2d(&tmB, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
+    if (rc != TT_OK) return rc;
+    GemmParams p;
+    default_params(p);
+    p.M = M; p.N = N; p.K = K;
+    p.C = (__nv_bfloat16*)c;
+    p.ldc = ldc;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.status = status;
+    p.a_mode = a_mode;
+    p.a_span = a_span;
+    p.a_row_off = a_row_off;
+    p.n_seg = segmented ? n : 1;
+    p.seg_rows = segmented ? seg_rows : M;
+    p.seg_rot = segmented ? my_rank : 0;       // own rows first: they need no peer traffic
+    p.my_rank = my_rank;
+    p.store_mode = store_mode;
+    p.out_span = out_span;
+    p.out_row_off = out_row_off;
+    p.out_ld = out_ld;
+    if (store_mode != 0)
+        for (int r = 0; r < n; ++r) p.peer_out[r] = (__nv_bfloat16*)out_ptrs[r];
+    p.tiles_m = p.n_seg * ((p.seg_rows + BM - 1) / BM);
+    p.tiles_n = (N + BN - 1) / BN;
+    cudaStream_t st = (cudaStream_t)stream;
+    return BN == 128 ? dispatch<128>(false, b_mn != 0, 0, tmA, tmB, p, sms, st)
+                     : dispatch<256>(false, b_mn != 0, 0, tmA, tmB, p, sms, st);
+}
+
+// QKV projection with everything after it fused into the epilogue: bias, QK-RMSNorm, RoPE, and the Ulysses
+// sequence -> head all-to-all (each 128-column tile is one head's q, k or v and is stored straight into the
+// [batch, heads_per_rank, s_out, 128] buffer of the rank that owns the head, at token offset out_off).
+//   x [M, K] local tokens (M = batch * s_in), w [heads*384, K] with rows ordered [head][q|k|v][128];
+//   q_ptrs / k_ptrs / v_ptrs [n]: destination buffers per owner rank (n = 1: local only);
+//   only_local != 0: compute every head but store only the heads this rank owns (replicated text tokens);
+//   aux (optional) [M, heads*384]: raw projection output, kept for the backward pass.
+extern "C" int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias, const void* qw, const void* kw,
+                                 const float* cos_t, const float* sin_t, void* const* q_ptrs, void* const* k_ptrs,
+                                 void* const* v_ptrs, int n, int my_rank, void* aux, int M, int heads, int K, int s_in,
+                                 int s_out, int out_off, int rope_len, int only_local, float eps, int* status,
+                                 void* stream) {
+    if (n < 1 || n > TT_MAX_PEERS || my_rank < 0 || my_rank >= n || M <= 0 || heads <= 0 || heads % n || (K & 7)) return TT_ERR_ARG;
+    if (s_in <= 0 || M % s_in || out_off < 0 || out_off + s_in > s_out || status == nullptr) return TT_ERR_ARG;
+    if (rope_len > 0 && (cos_t == nullptr || sin_t == nullptr)) return TT_ERR_ARG;
+    const int N = heads * 384;
+    TmapArray tmA;
+    CUtensorMap tmB;
+    int rc;
+    if ((rc = tt_make_tmap_2d(&tmA.m[0], x, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK)) != TT_OK) return rc;
+    if ((rc = tt_make_tmap_2d(&tmB, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128, BK)) != TT_OK) return rc;
+    GemmParams p;
+    default_params(p);
+    p.M = M; p.N = N; p.K = K;
+    p.ldc = N;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.aux = (__nv_bfloat16*)aux;
+    p.status = status;
+    p.seg_rows = M;
+    p.my_rank = my_rank;
+    p.qw = (const __nv_bfloat16*)qw;
+    p.kw = (const __nv_bfloat16*)kw;
+    p.cos_t = cos_t;
+    p.sin_t = sin_t;
+    p.eps = eps;
+    p.rope_len = rope_len;
+    p.heads_per_rank = heads / n;
+    p.s_in = s_in;
+    p.s_out = s_out;
+    p.out_off = out_off;
+    p.only_local = only_local;
+    for (int r = 0; r < n; ++r) {
+        p.peer_q[r] = (__nv_bfloat16*)q_ptrs[r];
+        p.peer_k[r] = (__nv_bfloat16*)k_ptrs[r];
+        p.peer_v[r] = (__nv_bfloat16*)v_ptrs[r];
+    }
+    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_n = N / 128;
+    return dispatch<128>(false, false, 5, tmA, tmB, p, sm_count(), (cudaStream_t)stream);
 }

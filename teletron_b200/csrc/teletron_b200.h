@@ -60,6 +60,16 @@ int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, voi
 int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
 
+/* GEMM fused with a collective over peer memory, and the fused QKV projection (see gemm_tcgen05.cu) */
+int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off, const void* b,
+                      int b_mn, long ldb, void* c, long ldc, const void* bias, int M, int N, int K, int seg_rows,
+                      int my_rank, int store_mode, void* const* out_ptrs, int out_span, int out_row_off, long out_ld,
+                      int* status, void* stream);
+int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias, const void* qw, const void* kw, const float* cos_t,
+                      const float* sin_t, void* const* q_ptrs, void* const* k_ptrs, void* const* v_ptrs, int n,
+                      int my_rank, void* aux, int M, int heads, int K, int s_in, int s_out, int out_off, int rope_len,
+                      int only_local, float eps, int* status, void* stream);
+
 /* ---- tcgen05 flash attention: q, k, v, dq, dk, dv [B*H, S, 128]; out, dout [B, S, H*128];
  *      lse, delta [B*H, pitch] fp32, pitch % 64 == 0, lse = +inf and delta = 0 at positions >= S ---- */
 int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int kv_len,
