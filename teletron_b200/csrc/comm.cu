@@ -116,6 +116,21 @@ __global__ void __launch_bounds__(256) partial_sum_kernel(const __nv_bfloat16* _
     }
 }
 
+// dst[row, r*span + c] = src_r[(row_off + row) * span + c]: the head -> sequence all-to-all as a plain copy
+// (each rank holds `span` columns for all rows; this rank collects its own rows from everyone)
+__global__ void __launch_bounds__(256) gather_cols_kernel(PeerTable src, int n, long rows, int span, long row_off,
+                                                         __nv_bfloat16* __restrict__ dst) {
+    const int nvec = span >> 3;
+    const long total = rows * n * nvec;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long row = i / ((long)n * nvec);
+        const int rem = (int)(i - row * n * nvec);
+        const int r = rem / nvec, c = rem - r * nvec;
+        const bf16x8 v = ld8(reinterpret_cast<const __nv_bfloat16*>(src.ptr[r]) + (row_off + row) * span + c * 8);
+        st8(dst + (row * n + r) * span + c * 8, v);
+    }
+}
+
 int fill_table(PeerTable& t, void* const* ptrs, int n) {
     if (n < 1 || n > TT_MAX_PEERS) return TT_ERR_ARG;
     for (int i = 0; i < TT_MAX_PEERS; ++i) t.ptr[i] = i < n ? ptrs[i] : nullptr;
@@ -204,6 +219,19 @@ extern "C" int tt_partial_sum(const void* stage, int n, long rows, int cols, con
     partial_sum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)stage, n, rows, cols, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)res,
         (const __nv_bfloat16*)gate, rows_per_batch > 0 ? rows_per_batch : rows, (__nv_bfloat16*)out);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+extern "C" int tt_gather_cols_bf16(void* const* src_ptrs, int n, long rows, int span, long row_off, void* dst,
+                                   void* stream) {
+    PeerTable t;
+    int rc = fill_table(t, src_ptrs, n);
+    if (rc != TT_OK || rows <= 0 || span <= 0 || (span & 7) || row_off < 0) return TT_ERR_ARG;
+    const long total = rows * n * (span >> 3);
+    long want = (total + 255) / 256;
+    const int grid = (int)(want < 148L * 8 ? want : 148L * 8);
+    gather_cols_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(t, n, rows, span, row_off, (__nv_bfloat16*)dst);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }

@@ -32,7 +32,7 @@ constexpr int kThreads = 192;
 constexpr int kGroupM = 16;
 
 struct TmapArray {
-    CUtensorMap m[TT_MAX_PEERS];
+    CUtensorMap m[TT_MAX_PEERS + 1];     // last slot: local tensor supplying the K columns beyond the gathered ones
 };
 
 struct GemmParams {
@@ -47,6 +47,7 @@ struct GemmParams {
     int a_mode;             // 0: one source; 1: source chosen by K column block (head -> owner rank);
                             // 2: source chosen by M segment (all-gather of row blocks)
     int a_span;             // mode 1: K columns held by each source
+    int a_nsrc;             // mode 1: number of sources; K columns >= a_nsrc * a_span come from the local extra tensor
     int a_row_off;          // mode 0/1: row offset of this rank's rows inside the source tensor
     int n_seg, seg_rows;    // M is n_seg segments of seg_rows rows (n_seg == 1: plain)
     int seg_rot;            // first segment processed (own rank's rows first)
@@ -55,6 +56,7 @@ struct GemmParams {
     int store_mode;         // 0: C (local); 1: column block -> peer_out[col / out_span] (head -> owner);
                             // 2: row segment -> peer_out[segment] staging slot of this rank (reduce-scatter push)
     int out_span, out_row_off;
+    int n_dest;             // store_mode 1: number of routed column blocks; later columns go to C
     long out_ld;
     __nv_bfloat16* peer_out[TT_MAX_PEERS];
     // ---- fused QKV epilogue (EPI 5): bias, QK-RMSNorm, RoPE, head-major scatter to the head's owner rank ----
@@ -167,8 +169,14 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                         int ak = k0, am = p.a_row_off + seg * p.seg_rows + m0;
                         if (p.a_mode == 1) {
                             const int src = k0 / p.a_span;
-                            ta = &tmA.m[src];
-                            ak = k0 - src * p.a_span;
+                            if (src < p.a_nsrc) {
+                                ta = &tmA.m[src];
+                                ak = k0 - src * p.a_span;
+                            } else {        // local tail (e.g. the MLP half of the single block's merged projection)
+                                ta = &tmA.m[TT_MAX_PEERS];
+                                ak = k0 - p.a_nsrc * p.a_span;
+                                am = m0;
+                            }
                         } else if (p.a_mode == 2) {
                             ta = &tmA.m[seg];
                             am = m0;
@@ -309,8 +317,13 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                     crow = p.C + (long)row * p.ldc;
                 } else if (p.store_mode == 1) {
                     const int dest = n0 / p.out_span;
-                    ccol = n0 - dest * p.out_span;
-                    crow = p.peer_out[dest] + (long)(p.out_row_off + row) * p.out_ld;
+                    if (dest < p.n_dest) {
+                        ccol = n0 - dest * p.out_span;
+                        crow = p.peer_out[dest] + (long)(p.out_row_off + row) * p.out_ld;
+                    } else {            // columns beyond the routed ones stay local
+                        ccol = n0 - p.n_dest * p.out_span;
+                        crow = p.C + (long)row * p.ldc;
+                    }
                 } else {
                     crow = p.peer_out[seg] + ((long)p.my_rank * p.seg_rows + lrow) * p.out_ld;
                 }
@@ -539,18 +552,23 @@ extern "C" int tt_gemm_bf16(const void* a, const void* b, void* c, const void* b
 //             row pitch out_ld): the sequence -> head all-to-all of a data gradient.  2: row segment i goes to
 //             out_ptrs[i] + my_rank * seg_rows * N: partial sums pushed to their owner (reduce-scatter; sum with
 //             tt_partial_sum after a barrier).
+//   a_extra (a_mode 1, optional): local [M, K - n * a_span] tensor (row pitch lda_extra) supplying the remaining K
+//             columns.  With store_mode 1, output columns beyond n * out_span are stored to c (row pitch ldc).
 extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off,
-                                 const void* b, int b_mn, long ldb, void* c, long ldc, const void* bias, int M, int N,
-                                 int K, int seg_rows, int my_rank, int store_mode, void* const* out_ptrs, int out_span,
-                                 int out_row_off, long out_ld, int* status, void* stream) {
+                                 const void* a_extra, long lda_extra, const void* b, int b_mn, long ldb, void* c,
+                                 long ldc, const void* bias, int M, int N, int K, int seg_rows, int my_rank,
+                                 int store_mode, void* const* out_ptrs, int out_span, int out_row_off, long out_ld,
+                                 int* status, void* stream) {
     if (n < 1 || n > TT_MAX_PEERS || M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7) || status == nullptr) return TT_ERR_ARG;
     if (a_mode < 0 || a_mode > 2 || store_mode < 0 || store_mode > 2 || my_rank < 0 || my_rank >= n) return TT_ERR_ARG;
-    if (a_mode == 1 && ((a_span % BK) || (long)a_span * n != K)) return TT_ERR_ARG;
+    if (a_mode == 1 && ((a_span % BK) || (long)a_span * n > K)) return TT_ERR_ARG;
+    if (a_mode == 1 && (long)a_span * n != K && a_extra == nullptr) return TT_ERR_ARG;
     const bool segmented = a_mode == 2 || store_mode == 2;
     if (segmented && (seg_rows <= 0 || (long)seg_rows * n != M)) return TT_ERR_ARG;
     if (store_mode == 0 && (c == nullptr || (ldc & 7))) return TT_ERR_ARG;
     if (store_mode != 0 && (out_ptrs == nullptr || (out_ld & 7))) return TT_ERR_ARG;
-    if (store_mode == 1 && (out_span <= 0 || (out_span % 128) || N % out_span)) return TT_ERR_ARG;
+    if (store_mode == 1 && (out_span <= 0 || (out_span % 128) || (long)out_span * n > N)) return TT_ERR_ARG;
+    if (store_mode == 1 && (long)out_span * n != N && (c == nullptr || (ldc & 7))) return TT_ERR_ARG;
     const int sms = sm_count();
     // a column block routed to one peer must not straddle two tiles' owners: 128-wide tiles when spans are 128-multiples
     const int BN = pick_bn(M, N, sms, store_mode == 1 && (out_span % 256) != 0);
@@ -562,6 +580,11 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
         const uint64_t rows = a_mode == 2 ? (uint64_t)seg_rows : (uint64_t)a_rows;
         const uint64_t cols = a_mode == 1 ? (uint64_t)a_span : (uint64_t)K;
         if ((rc = tt_make_tmap_2d(&tmA.m[r], a_ptrs[r], rows, cols, cols, BM, BK)) != TT_OK) return rc;
+    }
+    if (a_mode == 1 && a_extra != nullptr) {
+        const uint64_t cols = (uint64_t)K - (uint64_t)a_span * n;
+        if ((rc = tt_make_tmap_2d(&tmA.m[TT_MAX_PEERS], a_extra, (uint64_t)M, cols, (uint64_t)lda_extra, BM, BK)) != TT_OK)
+            return rc;
     }
     if (!b_mn) rc = tt_make_tmap_2d(&tmB, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, BK);
     else rc = tt_make_tmap_2d(&tmB, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
@@ -575,7 +598,9 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
     p.status = status;
     p.a_mode = a_mode;
     p.a_span = a_span;
+    p.a_nsrc = n;
     p.a_row_off = a_row_off;
+    p.n_dest = n;
     p.n_seg = segmented ? n : 1;
     p.seg_rows = segmented ? seg_rows : M;
     p.seg_rot = segmented ? my_rank : 0;       // own rows first: they need no peer traffic

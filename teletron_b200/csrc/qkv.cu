@@ -88,10 +88,19 @@ __global__ void __launch_bounds__(256) qkv_post_fwd_kernel(
     }
 }
 
+struct PeerTable3 {
+    const __nv_bfloat16* q[TT_MAX_PEERS];
+    const __nv_bfloat16* k[TT_MAX_PEERS];
+    const __nv_bfloat16* v[TT_MAX_PEERS];
+};
+
 // partials: [gridDim.x * warps][2][128] fp32 (dq-norm weight, dk-norm weight)
+// dq / dk / dv live head-sharded on the rank that owns each head ([batch, heads_per_rank, seq_out, 128]); with
+// more than one rank this kernel reads them over NVLink, which is the head -> sequence all-to-all of the
+// Ulysses backward fused with the RoPE transpose and the RMSNorm backward.
 __global__ void __launch_bounds__(256) qkv_post_bwd_kernel(
-    const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ dv,
-    const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+    const PeerTable3 src, const int heads_per_rank, const __nv_bfloat16* __restrict__ qkv,
+    const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ dqkv,
     float* __restrict__ partials, long rows, int heads, long seq_in, long seq_out, long out_offset, long rope_len,
     float eps) {
@@ -107,13 +116,14 @@ __global__ void __launch_bounds__(256) qkv_post_bwd_kernel(
         const int h = (int)(w - row * heads);
         const long b = row / seq_in, s = row - b * seq_in;
         const long off_in = (row * heads + h) * (3L * D) + lane * 4;
-        const long src = ((b * heads + h) * seq_out + out_offset + s) * D + lane * 4;
+        const int owner = h / heads_per_rank, hl = h - owner * heads_per_rank;
+        const long so = ((b * heads_per_rank + hl) * seq_out + out_offset + s) * D + lane * 4;
         float gq[4], gk[4], xq[4], xk[4];
-        ld4(dq + src, gq);
-        ld4(dk + src, gk);
+        ld4(src.q[owner] + so, gq);
+        ld4(src.k[owner] + so, gk);
         ld4(qkv + off_in, xq);
         ld4(qkv + off_in + D, xk);
-        *reinterpret_cast<uint2*>(dqkv + off_in + 2 * D) = *reinterpret_cast<const uint2*>(dv + src);
+        *reinterpret_cast<uint2*>(dqkv + off_in + 2 * D) = *reinterpret_cast<const uint2*>(src.v[owner] + so);
         if (s < rope_len) {        // transpose of the rotation
             const float4 c = *reinterpret_cast<const float4*>(cos_t + s * D + lane * 4);
             const float4 sn = *reinterpret_cast<const float4*>(sin_t + s * D + lane * 4);
@@ -204,22 +214,40 @@ extern "C" int tt_qkv_post_fwd(const void* qkv, const void* qw, const void* kw, 
     return TT_OK;
 }
 
-extern "C" int tt_qkv_post_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw,
-                               const void* kw, const float* cos_t, const float* sin_t, void* dqkv, float* partials,
-                               void* dqw, void* dkw, long rows, int heads, long seq_in, long seq_out, long out_offset,
-                               long rope_len, float eps, void* stream) {
+// dq_ptrs / dk_ptrs / dv_ptrs [n]: rank r's [batch, heads / n, seq_out, 128] gradient buffers (n = 1: local).
+extern "C" int tt_qkv_post_bwd_peer(void* const* dq_ptrs, void* const* dk_ptrs, void* const* dv_ptrs, int n,
+                                    const void* qkv, const void* qw, const void* kw, const float* cos_t,
+                                    const float* sin_t, void* dqkv, float* partials, void* dqw, void* dkw, long rows,
+                                    int heads, long seq_in, long seq_out, long out_offset, long rope_len, float eps,
+                                    void* stream) {
     if (rows <= 0 || heads <= 0 || seq_in <= 0 || rows % seq_in || out_offset < 0 || out_offset + seq_in > seq_out)
         return TT_ERR_ARG;
+    if (n < 1 || n > TT_MAX_PEERS || heads % n) return TT_ERR_ARG;
     if (rope_len > 0 && (cos_t == nullptr || sin_t == nullptr)) return TT_ERR_ARG;
+    PeerTable3 t;
+    for (int r = 0; r < TT_MAX_PEERS; ++r) {
+        t.q[r] = (const __nv_bfloat16*)(r < n ? dq_ptrs[r] : nullptr);
+        t.k[r] = (const __nv_bfloat16*)(r < n ? dk_ptrs[r] : nullptr);
+        t.v[r] = (const __nv_bfloat16*)(r < n ? dv_ptrs[r] : nullptr);
+    }
     cudaStream_t st = (cudaStream_t)stream;
     const int grid = pick_grid(rows * heads);
-    qkv_post_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk,
-                                              (const __nv_bfloat16*)dv, (const __nv_bfloat16*)qkv,
-                                              (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, cos_t, sin_t,
-                                              (__nv_bfloat16*)dqkv, partials, rows, heads, seq_in, seq_out, out_offset,
-                                              rope_len, eps);
+    qkv_post_bwd_kernel<<<grid, 256, 0, st>>>(t, heads / n, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)qw,
+                                              (const __nv_bfloat16*)kw, cos_t, sin_t, (__nv_bfloat16*)dqkv, partials,
+                                              rows, heads, seq_in, seq_out, out_offset, rope_len, eps);
     TT_CHECK_LAUNCH();
     qkv_weight_finalize_kernel<<<1, 256, 0, st>>>(partials, (__nv_bfloat16*)dqw, (__nv_bfloat16*)dkw, grid * 8);
     TT_CHECK_LAUNCH();
     return TT_OK;
+}
+
+extern "C" int tt_qkv_post_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, const void* qw,
+                               const void* kw, const float* cos_t, const float* sin_t, void* dqkv, float* partials,
+                               void* dqw, void* dkw, long rows, int heads, long seq_in, long seq_out, long out_offset,
+                               long rope_len, float eps, void* stream) {
+    void* q1[1] = {const_cast<void*>(dq)};
+    void* k1[1] = {const_cast<void*>(dk)};
+    void* v1[1] = {const_cast<void*>(dv)};
+    return tt_qkv_post_bwd_peer(q1, k1, v1, 1, qkv, qw, kw, cos_t, sin_t, dqkv, partials, dqw, dkw, rows, heads, seq_in,
+                                seq_out, out_offset, rope_len, eps, stream);
 }

@@ -47,6 +47,11 @@ int tt_qkv_post_bwd(const void* dq, const void* dk, const void* dv, const void* 
                     long rows, int heads, long seq_in, long seq_out, long out_offset, long rope_len, float eps,
                     void* stream);
 
+int tt_qkv_post_bwd_peer(void* const* dq_ptrs, void* const* dk_ptrs, void* const* dv_ptrs, int n, const void* qkv,
+                         const void* qw, const void* kw, const float* cos_t, const float* sin_t, void* dqkv,
+                         float* partials, void* dqw, void* dkw, long rows, int heads, long seq_in, long seq_out,
+                         long out_offset, long rope_len, float eps, void* stream);
+
 /* ---- activations ---- */
 int tt_gelu_fwd(const void* u, void* y, long n, int kind, void* stream);   /* kind 0 = erf, 1 = tanh */
 int tt_gelu_bwd(const void* dy, const void* u, void* du, long n, int kind, void* stream);
@@ -61,10 +66,10 @@ int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* 
                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
 
 /* GEMM fused with a collective over peer memory, and the fused QKV projection (see gemm_tcgen05.cu) */
-int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off, const void* b,
-                      int b_mn, long ldb, void* c, long ldc, const void* bias, int M, int N, int K, int seg_rows,
-                      int my_rank, int store_mode, void* const* out_ptrs, int out_span, int out_row_off, long out_ld,
-                      int* status, void* stream);
+int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off,
+                      const void* a_extra, long lda_extra, const void* b, int b_mn, long ldb, void* c, long ldc,
+                      const void* bias, int M, int N, int K, int seg_rows, int my_rank, int store_mode,
+                      void* const* out_ptrs, int out_span, int out_row_off, long out_ld, int* status, void* stream);
 int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias, const void* qw, const void* kw, const float* cos_t,
                       const float* sin_t, void* const* q_ptrs, void* const* k_ptrs, void* const* v_ptrs, int n,
                       int my_rank, void* aux, int M, int heads, int K, int s_in, int s_out, int out_off, int rope_len,
@@ -89,6 +94,7 @@ int tt_comm_barrier(void* const* flag_ptrs, int my_rank, int n, unsigned long lo
                     int* status, void* stream);
 int tt_reduce_scatter_bf16(void* const* src_ptrs, int n, long offset, void* out, long count, float scale, void* stream);
 int tt_all_gather_push_bf16(void* const* dst_ptrs, int n, long offset, const void* src, long count, void* stream);
+int tt_gather_cols_bf16(void* const* src_ptrs, int n, long rows, int span, long row_off, void* dst, void* stream);
 int tt_partial_sum(const void* stage, int n, long rows, int cols, const void* bias, const void* res, const void* gate,
                    long rows_per_batch, void* out, void* stream);
 

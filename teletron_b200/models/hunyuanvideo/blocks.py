@@ -193,6 +193,41 @@ def _ulysses_attention(q, k, v, tq, tk, tv, pad: Optional[SeqPad], kv_valid_len:
     return o_v, o_t.reshape(o_t.shape[0], T, -1)
 
 
+_FUSED_COMM = False
+_WORKSPACES = {}
+
+
+def set_fused_comm(enabled: bool) -> None:
+    """Route the Ulysses all-to-alls through the compute + collective fused kernels
+    (:mod:`teletron_b200.ops.fused_comm`) instead of NCCL ``all_to_all_single``."""
+    global _FUSED_COMM
+    _FUSED_COMM = bool(enabled)
+
+
+def fused_comm_enabled() -> bool:
+    return _FUSED_COMM
+
+
+def _use_fused(x: torch.Tensor, head_dim: int) -> bool:
+    return (_FUSED_COMM and ps.get_context_parallel_world_size() > 1 and x.is_cuda and x.dtype == torch.bfloat16
+            and x.shape[0] == 1 and head_dim == 128 and ops.get_impl() != "torch")
+
+
+def _workspace(heads_local: int, s: int, T: int):
+    from ...ops.fused_comm import UlyssesWorkspace
+    key = (heads_local, s, T)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = _WORKSPACES[key] = UlyssesWorkspace(ps.get_context_parallel_group(), heads_local, s, T)
+    return ws
+
+
+def _fused_kv_len(ws, pad: Optional[SeqPad], kv_valid_len) -> Optional[int]:
+    if kv_valid_len is not None:
+        raise NotImplementedError("the text key mask is not available together with --fused-comm")
+    return None if pad is None or pad.pad == 0 else ws.T + pad.origin
+
+
 class JointAttention(nn.Module):
     """Dual-stream attention: separate QKV / out projections for video and text tokens."""
 
@@ -214,6 +249,8 @@ class JointAttention(nn.Module):
         tpg = ps.get_tensor_model_parallel_group()
         x = M.copy_to_tensor_model_parallel_region(x, tpg)
         ctx = M.copy_to_tensor_model_parallel_region(ctx, tpg)
+        if _use_fused(x, self.head_dim):
+            return self._forward_fused(x, ctx, cos, sin, pad, kv_valid_len)
         if ps.get_context_parallel_world_size() == 1:
             q, k, v = ops.joint_qkv_projection(
                 x, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight, self.k_layernorm.weight,
@@ -226,6 +263,31 @@ class JointAttention(nn.Module):
                                         self.added_q_layernorm.weight, self.added_k_layernorm.weight,
                                         None, None, self.heads_local, self.eps)
         return _ulysses_attention(q, k, v, tq, tk, tv, pad, kv_valid_len)
+
+
+    def _forward_fused(self, x, ctx, cos, sin, pad, kv_valid_len):
+        """QKV GEMM -> (RMSNorm, RoPE, seq->head all-to-all in the epilogue) -> attention; the caller finishes with
+        :meth:`project_fused` (head->seq all-to-all inside the output projections)."""
+        from ...ops import fused_comm as FC
+        ws = _workspace(self.heads_local, x.shape[1], ctx.shape[1])
+        q, k, v = FC.fused_qkv_a2a(ws, x, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight,
+                                   self.k_layernorm.weight, cos, sin, ctx, self.added_linear_qkv.weight,
+                                   self.added_linear_qkv.bias, self.added_q_layernorm.weight,
+                                   self.added_k_layernorm.weight, self.eps)
+        o = ops.attention(q, k, v, kv_valid_len=_fused_kv_len(ws, pad, kv_valid_len))
+        return ("fused", ws, o), None
+
+    def project_fused(self, handle):
+        from ...ops import fused_comm as FC
+        _, ws, o = handle
+        tp = self.linear_proj.tp
+        y, yt = FC.fused_a2a_linear(ws, o, self.linear_proj.weight, self.linear_proj.bias if tp == 1 else None,
+                                    self.added_linear_proj.weight, self.added_linear_proj.bias if tp == 1 else None)
+        if tp > 1:
+            g = ps.get_tensor_model_parallel_group()
+            y = M.reduce_from_tensor_model_parallel_region(y, g) + self.linear_proj.bias
+            yt = M.reduce_from_tensor_model_parallel_region(yt, g) + self.added_linear_proj.bias
+        return y, yt
 
 
 class SingleAttention(nn.Module):
@@ -276,8 +338,11 @@ class HunyuanDiTLayer(nn.Module):
         xn = ops.layernorm_modulate(x, scale_msa, shift_msa, self.eps)
         cn = ops.layernorm_modulate(ctx, c_scale_msa, c_shift_msa, self.eps)
         attn, c_attn = self.self_attention(xn, cn, cos, sin, pad, kv_valid_len)
-        a = self.self_attention.linear_proj(attn)
-        ca = self.self_attention.added_linear_proj(c_attn)
+        if isinstance(attn, tuple):
+            a, ca = self.self_attention.project_fused(attn)
+        else:
+            a = self.self_attention.linear_proj(attn)
+            ca = self.self_attention.added_linear_proj(c_attn)
         # residual update and the next LayerNorm + modulation in one pass over the tokens
         x, xn = ops.gate_residual_layernorm_modulate(x, a, gate_msa, scale_mlp, shift_mlp, self.eps)
         ctx, cn = ops.gate_residual_layernorm_modulate(ctx, ca, c_gate_msa, c_scale_mlp, c_shift_mlp, self.eps)
@@ -308,10 +373,35 @@ class HunyuanSingleDiTLayer(nn.Module):
         shift, scale, gate = self.norm(temb)
         hn = ops.layernorm_modulate(h, scale, shift, self.eps)
         mlp = self.proj_mlp(hn, activation=self.activation)
-        attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len)
-        merged = torch.cat([torch.cat([attn, c_attn], dim=1), mlp], dim=2)
-        h = ops.gate_residual(h, self.proj_out(merged), gate)
+        if _use_fused(hn, self.self_attention.head_dim):
+            proj = self._attention_and_projection_fused(hn, mlp, T, cos, sin, pad, kv_valid_len)
+        else:
+            attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len)
+            merged = torch.cat([torch.cat([attn, c_attn], dim=1), mlp], dim=2)
+            proj = self.proj_out(merged)
+        h = ops.gate_residual(h, proj, gate)
         return h[:, :-T], h[:, -T:]
+
+    def _attention_and_projection_fused(self, hn, mlp, T, cos, sin, pad, kv_valid_len):
+        """Single-stream block with both Ulysses all-to-alls fused: the QKV epilogue scatters heads to their owners and
+        the merged projection gathers them back per K block, taking the MLP half of its input from local memory."""
+        from ...ops import fused_comm as FC
+        sa = self.self_attention
+        s = hn.shape[1] - T
+        ws = _workspace(sa.heads_local, s, T)
+        hn = M.copy_to_tensor_model_parallel_region(hn, ps.get_tensor_model_parallel_group())
+        xv, xt = hn[:, :s], hn[:, s:]
+        w, b = sa.linear_qkv.weight, sa.linear_qkv.bias
+        q, k, v = FC.fused_qkv_a2a(ws, xv, w, b, sa.q_layernorm.weight, sa.k_layernorm.weight, cos, sin,
+                                   xt, w, b, sa.q_layernorm.weight, sa.k_layernorm.weight, sa.eps)
+        o = ops.attention(q, k, v, kv_valid_len=_fused_kv_len(ws, pad, kv_valid_len))
+        tp = self.proj_out.tp
+        wo, bo = self.proj_out.weight, (self.proj_out.bias if tp == 1 else None)
+        y, yt = FC.fused_a2a_linear(ws, o, wo, bo, wo, bo, extra=mlp[:, :s], extra_t=mlp[:, s:])
+        proj = torch.cat([y, yt], dim=1)
+        if tp > 1:
+            proj = M.reduce_from_tensor_model_parallel_region(proj, ps.get_tensor_model_parallel_group()) + self.proj_out.bias
+        return proj
 
 
 class AdaLNContinuous(nn.Module):

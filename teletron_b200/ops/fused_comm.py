@@ -1,0 +1,314 @@
+"""Compute + collective fused ops over the symmetric heap (NVLink peer loads / stores from inside the kernels).
+
+* :class:`UlyssesWorkspace` + :func:`fused_qkv_a2a` - QKV GEMM whose epilogue applies bias, QK-RMSNorm and RoPE
+  and stores every head tile straight into the buffer of the context-parallel rank that owns the head (the
+  sequence -> head all-to-all of ``dit_attention.py:277-279`` fused into the GEMM).  Backward: the inverse
+  all-to-all is fused into the RoPE-transpose / RMSNorm-backward kernel, which reads dq / dk / dv from their owners.
+* :func:`fused_a2a_linear` - output projection whose A operand is fetched per head from the rank that computed
+  that head's attention output (the head -> sequence all-to-all of ``dit_attention.py:325`` fused into the GEMM's
+  TMA loads).  Backward: the data-gradient GEMM pushes each head's columns to the head's owner.
+* :func:`fused_all_gather_linear` / :func:`fused_linear_reduce_scatter` - tensor-parallel all-gather -> GEMM and
+  GEMM -> reduce-scatter on sequence-sharded activations.
+* :func:`fused_grad_reduce_scatter` / :func:`fused_param_all_gather` - data-parallel gradient reduce-scatter with the
+  1/(dp*cp) scale folded in, and the parameter all-gather by peer stores.
+
+All of them take micro-batch 1 (the only mode the reference's launch scripts use).  Every cross-rank hand-over is
+a bounded device-side barrier on the heap (:meth:`SymmetricHeap.barrier`); call ``heap.check()`` at a
+synchronisation point to turn a timed-out barrier into :class:`CommTimeoutError`.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.symm_mem import SymmetricHeap
+from . import _lib, gemm
+from ._lib import c_float, c_int, c_long, call, check, ptr, stream
+from .gemm_tcgen05 import status_tensor
+
+BF16 = torch.bfloat16
+
+
+def _table(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+class UlyssesWorkspace:
+    """Symmetric buffers of one context-parallel group for a fixed (heads, local sequence, text length)."""
+
+    def __init__(self, group, heads: int, s_local: int, text_len: int, device=None, heap: Optional[SymmetricHeap] = None):
+        self.group = group
+        self.cp = 1 if group is None else dist.get_world_size(group)
+        self.rank = 0 if group is None else dist.get_rank(group)
+        if heads % self.cp:
+            raise ValueError(f"{heads} heads cannot be split over {self.cp} context-parallel ranks")
+        self.heads, self.h_loc = heads, heads // self.cp
+        self.s, self.T = s_local, text_len
+        self.S = self.cp * s_local
+        self.S_tot = self.S + text_len
+        # token order inside the buffers: [text | video of rank 0 | video of rank 1 | ...].  Text goes first so
+        # that context-parallel padding (at the end of the last rank's video tokens) is the tail of the sequence
+        # and a plain key-length mask removes it.
+        self.text_off = 0
+        self.video_off = text_len
+        n_qkv = self.h_loc * self.S_tot * 128 * 2                  # bytes of one of q / k / v (batch 1)
+        total = 8 * (n_qkv + 1024)
+        self.heap = heap or SymmetricHeap(group, total, device)
+        names = ("q", "k", "v", "o", "dq", "dk", "dv", "do")
+        self.off = {n: self.heap.alloc(n_qkv) for n in names}
+
+    def head_major(self, name: str, rank: Optional[int] = None) -> torch.Tensor:
+        return self.heap.tensor(self.off[name], (1, self.h_loc, self.S_tot, 128), BF16, rank)
+
+    def token_major(self, name: str, rank: Optional[int] = None) -> torch.Tensor:
+        return self.heap.tensor(self.off[name], (1, self.S_tot, self.h_loc * 128), BF16, rank)
+
+    def table(self, name: str):
+        return self.heap.ptr_table(self.off[name])
+
+    def local_table(self, name: str):
+        """Every slot points at this rank's buffer (stores that must stay local)."""
+        p = self.heap.local_ptr + self.off[name]
+        return _table([p] * self.cp)
+
+
+# ---------------------------------------------------------------------------------------------
+# F1: QKV GEMM + QK-RMSNorm + RoPE + sequence -> head all-to-all
+# ---------------------------------------------------------------------------------------------
+
+def _qkv_fused_launch(ws: UlyssesWorkspace, x2, w, b, qw, kw, cos, sin, out_off, rope_len, only_local, aux, names=("q", "k", "v")):
+    M, K = x2.shape
+    tabs = [ws.local_table(n) if only_local else ws.table(n) for n in names]
+    call("tt_qkv_gemm_fused", ptr(x2), ptr(w), ptr(b), ptr(qw), ptr(kw), ptr(cos), ptr(sin), tabs[0], tabs[1], tabs[2],
+         c_int(ws.cp), c_int(ws.rank), ptr(aux), c_int(M), c_int(ws.heads), c_int(K), c_int(M), c_int(ws.S_tot),
+         c_int(out_off), c_int(rope_len), c_int(1 if only_local else 0), c_float(1e-6), ptr(status_tensor(x2.device)),
+         stream())
+
+
+class _FusedQKVAllToAll(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ws, eps, cos, sin, x, w, b, qw, kw, xt, wt, bt, qwt, kwt):
+        s, T = x.shape[1], xt.shape[1]
+        if x.shape[0] != 1 or s != ws.s or T != ws.T:
+            raise _lib.NativeError("fused Ulysses ops take micro-batch 1 and the workspace's sequence lengths")
+        x2 = check(x.reshape(s, -1).contiguous(), BF16, "x")
+        xt2 = check(xt.reshape(T, -1).contiguous(), BF16, "xt")
+        cosf = check(cos.float().contiguous(), torch.float32, "cos")
+        sinf = check(sin.float().contiguous(), torch.float32, "sin")
+        need_grad = any(ctx.needs_input_grad)
+        aux = torch.empty(s, ws.heads * 384, dtype=BF16, device=x.device) if need_grad else None
+        auxt = torch.empty(T, ws.heads * 384, dtype=BF16, device=x.device) if need_grad else None
+        ws.heap.barrier()          # peers have finished reading q / k / v of the previous use
+        _qkv_fused_launch(ws, x2, w, b, qw, kw, cosf, sinf, ws.video_off + ws.rank * s, s, False, aux)
+        _qkv_fused_launch(ws, xt2, wt, bt, qwt, kwt, None, None, ws.text_off, 0, True, auxt)
+        ws.heap.barrier()          # every rank's tiles have landed
+        ctx.ws, ctx.eps = ws, eps
+        ctx.save_for_backward(x2, xt2, aux, auxt, cosf, sinf, w, qw, kw, wt, qwt, kwt)
+        ctx.has_bias = (b is not None, bt is not None)
+        ctx.shapes = (x.shape, xt.shape)
+        q, k, v = (ws.head_major(n) for n in ("q", "k", "v"))
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        ws: UlyssesWorkspace = ctx.ws
+        x2, xt2, aux, auxt, cosf, sinf, w, qw, kw, wt, qwt, kwt = ctx.saved_tensors
+        s, T = ws.s, ws.T
+        ws.heap.barrier()          # previous readers of the gradient buffers are done
+        for name, g in (("dq", dq), ("dk", dk), ("dv", dv)):
+            dst = ws.head_major(name)
+            if g.data_ptr() != dst.data_ptr():
+                dst.copy_(g)
+        ws.heap.barrier()          # every rank's head-sharded gradients are in place
+        outs = []
+        for (xx, raw, ww, q_w, k_w, off, rl, scale, hb) in ((x2, aux, w, qw, kw, ws.video_off + ws.rank * s, s, 1.0, ctx.has_bias[0]),
+                                                        (xt2, auxt, wt, qwt, kwt, ws.text_off, 0, 1.0 / ws.cp, ctx.has_bias[1])):
+            rows = raw.shape[0]
+            dqkv = torch.empty_like(raw)
+            nw = _lib.lib().tt_qkv_partial_warps(c_long(rows), c_int(ws.heads))
+            partials = torch.empty(nw * 256, dtype=torch.float32, device=raw.device)
+            dqw = torch.empty(128, dtype=BF16, device=raw.device)
+            dkw = torch.empty_like(dqw)
+            call("tt_qkv_post_bwd_peer", ws.table("dq"), ws.table("dk"), ws.table("dv"), c_int(ws.cp), ptr(raw),
+                 ptr(q_w.contiguous()), ptr(k_w.contiguous()), ptr(cosf if rl else None), ptr(sinf if rl else None),
+                 ptr(dqkv), ptr(partials), ptr(dqw), ptr(dkw), c_long(rows), c_int(ws.heads), c_long(rows),
+                 c_long(ws.S_tot), c_long(off), c_long(rl), c_float(ctx.eps), stream())
+            if scale != 1.0:
+                # replicated text tokens: every rank rebuilds the full gradient; the 1/cp keeps the DP x CP average exact
+                dqkv.mul_(scale)
+                dqw.mul_(scale)
+                dkw.mul_(scale)
+            dx = gemm.gemm_nn(dqkv, ww)
+            dw = gemm.gemm_tn(dqkv, xx)
+            db = dqkv.sum(dim=0, dtype=torch.float32).to(BF16) if hb else None
+            outs.append((dx, dw, db, dqw, dkw))
+        (dx, dw, db, dqw, dkw), (dxt, dwt, dbt, dqwt, dkwt) = outs
+        xs, xts = ctx.shapes
+        return (None, None, None, None, dx.view(xs), dw, db, dqw, dkw, dxt.view(xts), dwt, dbt, dqwt, dkwt)
+
+
+def fused_qkv_a2a(ws: UlyssesWorkspace, x, w, b, qw, kw, cos, sin, xt, wt, bt, qwt, kwt, eps: float = 1e-6):
+    """Video tokens ``x [1, s, H]`` (sequence-sharded, RoPE applied) and replicated text tokens ``xt [1, T, H]`` ->
+    ``q, k, v [1, heads / cp, T + cp * s, 128]`` for this rank's heads over the whole sequence (text tokens first)."""
+    return _FusedQKVAllToAll.apply(ws, eps, cos, sin, x, w, b, qw, kw, xt, wt, bt, qwt, kwt)
+
+
+# ---------------------------------------------------------------------------------------------
+# F2: head -> sequence all-to-all + output projection
+# ---------------------------------------------------------------------------------------------
+
+def _a2a_gemm(ws: UlyssesWorkspace, src_name: str, row_off: int, M: int, w, bias, extra=None):
+    N, K = w.shape
+    out = torch.empty(M, N, dtype=BF16, device=w.device)
+    call("tt_gemm_comm_bf16", ws.table(src_name), c_int(ws.cp), c_int(1), c_long(ws.S_tot), c_int(ws.h_loc * 128),
+         c_int(row_off), ptr(extra), c_long(0 if extra is None else extra.stride(0)), ptr(w), c_int(0), c_long(w.stride(0)),
+         ptr(out), c_long(N), ptr(bias), c_int(M), c_int(N), c_int(K), c_int(0), c_int(ws.rank), c_int(0), None, c_int(0),
+         c_int(0), c_long(0), ptr(status_tensor(w.device)), stream())
+    return out
+
+
+class _FusedAllToAllLinear(torch.autograd.Function):
+    """``y_video = gather_heads(o)[rank's tokens] @ W^T + b`` and ``y_text = gather_heads(o)[text] @ Wt^T + bt`` with the
+    gather fused into the GEMM operand fetch.  ``extra`` / ``extra_t`` are optional local tensors concatenated to
+    the gathered heads along K (the MLP half of the single block's merged projection)."""
+
+    @staticmethod
+    def forward(ctx, ws, o, w, b, wt, bt, extra, extra_t):
+        dst = ws.token_major("o")
+        ws.heap.barrier()                      # peers are done with the previous contents of `o`
+        if o.data_ptr() != dst.data_ptr():
+            dst.copy_(o)
+        ws.heap.barrier()
+        ex = None if extra is None else check(extra.reshape(ws.s, -1).contiguous(), BF16, "extra")
+        ext = None if extra_t is None else check(extra_t.reshape(ws.T, -1).contiguous(), BF16, "extra_t")
+        y = _a2a_gemm(ws, "o", ws.video_off + ws.rank * ws.s, ws.s, w, b, ex)
+        yt = _a2a_gemm(ws, "o", ws.text_off, ws.T, wt, bt, ext)
+        ctx.ws = ws
+        ctx.save_for_backward(w, wt, ex, ext)
+        ctx.has = (b is not None, bt is not None, extra is not None, extra_t is not None)
+        ctx.extra_shapes = (None if extra is None else extra.shape, None if extra_t is None else extra_t.shape)
+        return y.view(1, ws.s, -1), yt.view(1, ws.T, -1)
+
+    @staticmethod
+    def backward(ctx, dy, dyt):
+        ws: UlyssesWorkspace = ctx.ws
+        w, wt, ex, ext = ctx.saved_tensors
+        hb, hbt, hex_, hext = ctx.has
+        span = ws.h_loc * 128
+        G = ws.cp * span                                        # gathered K columns
+        dy2 = check(dy.reshape(ws.s, -1).contiguous(), BF16, "dy")
+        dyt2 = check(dyt.reshape(ws.T, -1).contiguous(), BF16, "dyt")
+        dev = dy2.device
+        # weight gradients need the gathered activations: collect them with the peer-reading copy kernel
+        a = torch.empty(ws.s, G, dtype=BF16, device=dev)
+        call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(ws.s), c_int(span), c_long(ws.video_off + ws.rank * ws.s), ptr(a), stream())
+        at = torch.empty(ws.T, G, dtype=BF16, device=dev)
+        call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(ws.T), c_int(span), c_long(ws.text_off), ptr(at), stream())
+        a_full = a if ex is None else torch.cat([a, ex], dim=1)
+        at_full = at if ext is None else torch.cat([at, ext], dim=1)
+        dw = gemm.gemm_tn(dy2, a_full)
+        dwt = gemm.gemm_tn(dyt2, at_full)
+        db = dy2.sum(0, dtype=torch.float32).to(BF16) if hb else None
+        dbt = dyt2.sum(0, dtype=torch.float32).to(BF16) if hbt else None
+        # data gradient: each head's columns go to the head's owner (sequence -> head all-to-all fused in the epilogue)
+        K = w.shape[1]
+        dex = torch.empty(ws.s, K - G, dtype=BF16, device=dev) if hex_ else None
+        ws.heap.barrier()                      # peers are done reading the previous contents of `do`
+        call("tt_gemm_comm_bf16", _table([dy2.data_ptr()]), c_int(ws.cp), c_int(0), c_long(ws.s), c_int(0), c_int(0), None,
+             c_long(0), ptr(w), c_int(1), c_long(w.stride(0)), ptr(dex), c_long(0 if dex is None else dex.stride(0)), None,
+             c_int(ws.s), c_int(K), c_int(w.shape[0]), c_int(0), c_int(ws.rank), c_int(1), ws.table("do"), c_int(span),
+             c_int(ws.video_off + ws.rank * ws.s), c_long(span), ptr(status_tensor(dev)), stream())
+        # text rows: every rank holds the full gradient; keep this rank's heads, scaled by cp (the gather's "up" rule)
+        dot_full = gemm.gemm_nn(dyt2, wt)
+        do_local = ws.token_major("do")
+        do_local[0, ws.text_off:ws.text_off + ws.T, :].copy_(dot_full[:, ws.rank * span:(ws.rank + 1) * span] * float(ws.cp))
+        dext = dot_full[:, G:].contiguous().view(ctx.extra_shapes[1]) if hext else None
+        ws.heap.barrier()                      # all pushed gradient tiles have landed
+        return (None, do_local, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
+
+
+def fused_a2a_linear(ws: UlyssesWorkspace, o, w, b, wt, bt, extra=None, extra_t=None):
+    """``o [1, S_tot, heads/cp * 128]`` (this rank's heads, all tokens) -> projections of this rank's video tokens
+    (weights ``w``) and of the replicated text tokens (weights ``wt``)."""
+    return _FusedAllToAllLinear.apply(ws, o, w, b, wt, bt, extra, extra_t)
+
+
+# ---------------------------------------------------------------------------------------------
+# F3: tensor-parallel all-gather -> GEMM and GEMM -> reduce-scatter
+# ---------------------------------------------------------------------------------------------
+
+class TPWorkspace:
+    """Symmetric staging for sequence-sharded tensor parallelism: a gather source and a reduce-scatter landing zone."""
+
+    def __init__(self, group, rows_local: int, k_max: int, n_max: int, device=None):
+        self.group = group
+        self.tp = 1 if group is None else dist.get_world_size(group)
+        self.rank = 0 if group is None else dist.get_rank(group)
+        self.rows = rows_local
+        a_bytes = rows_local * k_max * 2
+        s_bytes = self.tp * rows_local * n_max * 2
+        self.heap = SymmetricHeap(group, a_bytes + s_bytes + 4096, device)
+        self.off_a = self.heap.alloc(a_bytes)
+        self.off_s = self.heap.alloc(s_bytes)
+        self.k_max, self.n_max = k_max, n_max
+
+
+def fused_all_gather_linear(ws: TPWorkspace, x_local: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+    """``all_gather(x_local over rows) @ w^T + bias``: every rank's row block is TMA-loaded from its owner while the
+    tensor core works; this rank's own rows are scheduled first.  ``x_local [rows, K]``, ``w [N, K]`` (column-parallel shard)."""
+    rows, K = x_local.shape
+    if rows != ws.rows or K > ws.k_max:
+        raise _lib.NativeError("operand does not match the workspace")
+    src = ws.heap.tensor(ws.off_a, (rows, K), BF16)
+    ws.heap.barrier()
+    src.copy_(x_local)
+    ws.heap.barrier()
+    N = w.shape[0]
+    M = rows * ws.tp
+    out = torch.empty(M, N, dtype=BF16, device=w.device)
+    call("tt_gemm_comm_bf16", ws.heap.ptr_table(ws.off_a), c_int(ws.tp), c_int(2), c_long(rows), c_int(0), c_int(0), None,
+         c_long(0), ptr(w), c_int(0), c_long(w.stride(0)), ptr(out), c_long(N), ptr(bias), c_int(M), c_int(N), c_int(K),
+         c_int(rows), c_int(ws.rank), c_int(0), None, c_int(0), c_int(0), c_long(0), ptr(status_tensor(w.device)), stream())
+    return out
+
+
+def fused_linear_reduce_scatter(ws: TPWorkspace, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, gate=None) -> torch.Tensor:
+    """``reduce_scatter(x @ w^T over rows) + bias`` (optionally ``residual + gate * (...)``): every rank multiplies its K
+    shard for all rows and pushes each row block's partial tile to the block's owner from the GEMM epilogue; the
+    owner then sums the ``tp`` partials.  ``x [tp * rows, K_shard]``, ``w [N, K_shard]``; returns ``[rows, N]``."""
+    M, K = x.shape
+    N = w.shape[0]
+    if M != ws.rows * ws.tp or N > ws.n_max:
+        raise _lib.NativeError("operand does not match the workspace")
+    ws.heap.barrier()              # previous partials have been consumed everywhere
+    call("tt_gemm_comm_bf16", _table([x.data_ptr()]), c_int(ws.tp), c_int(0), c_long(M), c_int(0), c_int(0), None, c_long(0),
+         ptr(w), c_int(0), c_long(w.stride(0)), None, c_long(0), None, c_int(M), c_int(N), c_int(K), c_int(ws.rows),
+         c_int(ws.rank), c_int(2), ws.heap.ptr_table(ws.off_s), c_int(0), c_int(0), c_long(N), ptr(status_tensor(x.device)),
+         stream())
+    ws.heap.barrier()              # all partials have landed
+    out = torch.empty(ws.rows, N, dtype=BF16, device=x.device)
+    stage = ws.heap.tensor(ws.off_s, (ws.tp, ws.rows, N), BF16)
+    call("tt_partial_sum", ptr(stage), c_int(ws.tp), c_long(ws.rows), c_int(N), ptr(bias), ptr(residual), ptr(gate),
+         c_long(ws.rows), ptr(out), stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# F4: data-parallel gradient reduce-scatter (+ scale) and parameter all-gather over peer memory
+# ---------------------------------------------------------------------------------------------
+
+def fused_grad_reduce_scatter(heap: SymmetricHeap, grad_off: int, start: int, count: int, out: torch.Tensor, scale: float) -> None:
+    """``out[:] = scale * sum_r grad_r[start : start + count]`` reading every rank's bf16 gradient buffer (which lives
+    in the heap at ``grad_off``) with peer loads.  The caller brackets it with ``heap.barrier()``."""
+    call("tt_reduce_scatter_bf16", heap.ptr_table(grad_off), c_int(heap.world), c_long(start), ptr(out), c_long(count),
+         c_float(scale), stream())
+
+
+def fused_param_all_gather(heap: SymmetricHeap, param_off: int, start: int, src: torch.Tensor) -> None:
+    """Write this rank's updated parameter shard into every rank's parameter buffer at ``start``."""
+    call("tt_all_gather_push_bf16", heap.ptr_table(param_off), c_int(heap.world), c_long(start), ptr(src),
+         c_long(src.numel()), stream())
