@@ -43,6 +43,7 @@ class HunyuanParams:
     recompute_granularity: Optional[str] = None      # None | "full" | "selective"
     recompute_method: str = "block"                  # "block" | "uniform"
     recompute_num_layers: Optional[int] = None       # None = every block (reference behaviour)
+    recompute_save_attention: bool = False           # keep attention (out, lse) so the recompute pass skips that kernel
     fused_kernels: bool = True
     init_method_std: float = 0.006
     apply_text_mask: bool = False                    # reference never applies it (dit_attention.py:313)

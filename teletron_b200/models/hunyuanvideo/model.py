@@ -119,7 +119,10 @@ class HunyuanVideoTransformer3DModel(nn.Module):
                 return x, ctx
             limit = n if cfg.recompute_num_layers is None else min(n, cfg.recompute_num_layers)
             for i, b in enumerate(blocks):
-                if i < limit:
+                if i < limit and cfg.recompute_save_attention:
+                    from ...training.recompute import checkpoint_block
+                    x, ctx = checkpoint_block(b, (x, ctx, temb, cos, sin), (pad, kv_valid_len), save_attention=True)
+                elif i < limit:
                     x, ctx = checkpoint(b, x, ctx, temb, cos, sin, pad, kv_valid_len,
                                         use_reentrant=False, preserve_rng_state=False)
                 else:

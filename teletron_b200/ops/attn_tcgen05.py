@@ -7,6 +7,7 @@ to 64 and ``+inf`` in the padding) that the backward uses.
 
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Optional
 
@@ -37,10 +38,41 @@ def forward(q, k, v, kv_valid_len: Optional[int], scale: Optional[float]):
     return out, lse, q, k, v, sc, kv_len
 
 
+_CACHE = None
+_CACHE_MODE = None
+
+
+@contextlib.contextmanager
+def attention_cache(store: list, mode: str):
+    """``mode="record"``: append every attention call's (out, lse) to ``store``; ``mode="replay"``: consume them in the
+    same order instead of running the forward kernel (used by the block checkpoint that keeps attention outputs)."""
+    global _CACHE, _CACHE_MODE
+    prev = (_CACHE, _CACHE_MODE)
+    _CACHE, _CACHE_MODE = store, mode
+    try:
+        yield
+    finally:
+        _CACHE, _CACHE_MODE = prev
+
+
+def _forward_cached(q, k, v, kv_valid_len, scale):
+    if _CACHE_MODE == "replay" and _CACHE:
+        out, lse = _CACHE.pop(0)
+        B, H, S, D = q.shape
+        q, k, v = (check(t.contiguous(), BF16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+        sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+        kv_len = S if kv_valid_len is None else min(int(kv_valid_len), S)
+        return out, lse, q, k, v, sc, kv_len
+    res = forward(q, k, v, kv_valid_len, scale)
+    if _CACHE_MODE == "record":
+        _CACHE.append((res[0], res[1]))
+    return res
+
+
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, kv_valid_len, scale):
-        out, lse, qc, kc, vc, sc, kv_len = forward(q, k, v, kv_valid_len, scale)
+        out, lse, qc, kc, vc, sc, kv_len = _forward_cached(q, k, v, kv_valid_len, scale)
         ctx.save_for_backward(qc, kc, vc, out, lse)
         ctx.sc, ctx.kv_len = sc, kv_len
         return out

@@ -57,6 +57,9 @@ def _add_train_args(p):
     g.add_argument("--recompute-granularity", type=str, default=None, choices=["full", "selective"])
     g.add_argument("--recompute-method", type=str, default="block", choices=["uniform", "block"])
     g.add_argument("--recompute-num-layers", type=int, default=None)
+    g.add_argument("--recompute-save-attention", action="store_true",
+                   help="with full recompute, keep each block's attention output + log-sum-exp so the recompute pass "
+                        "replays attention instead of running it again")
     g.add_argument("--use-distributed-optimizer", action="store_true")
     g.add_argument("--overlap-grad-reduce", action="store_true")
     g.add_argument("--ddp-bucket-size", type=int, default=None, help="bucket size in elements")

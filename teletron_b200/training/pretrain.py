@@ -79,6 +79,9 @@ def initialize(extra_args_provider: Optional[Callable] = None, argv=None, args_d
                                  timeout_minutes=args.distributed_timeout_minutes)
     if ps.is_dit_rank():
         set_random_seed(args.seed, args.data_parallel_random_init)
+    if args.fused_comm:
+        from ..models.hunyuanvideo import blocks
+        blocks.set_fused_comm(True)
     args.device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
     return args
 

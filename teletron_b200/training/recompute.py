@@ -1,0 +1,60 @@
+"""Activation recomputation per transformer block.
+
+The reference checkpoints every block with Megatron's ``tensor_parallel.checkpoint`` (full recompute,
+``teletron/models/hunyuanvideo/model.py:216-238``): the whole block, attention included, runs twice.  Here
+:func:`checkpoint_block` does the same but can keep the attention kernel's output and log-sum-exp from the first
+pass (``save_attention=True``): the recompute pass then rebuilds every cheap activation and *replays* attention from
+the saved pair instead of running the most expensive kernel of the block a second time.  On a 180 GB B200 the
+extra ~0.2 GB per block at 32 k tokens is affordable and removes one of the 4.5 attention passes of a training step.
+
+No RNG state is captured: the blocks contain no dropout.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List
+
+import torch
+
+from ..ops import attn_tcgen05
+
+
+class _CheckpointBlock(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, run_fn: Callable, save_attention: bool, n_tensors: int, *args):
+        tensors, extra = args[:n_tensors], args[n_tensors:]
+        ctx.run_fn, ctx.extra = run_fn, extra
+        ctx.requires = [t.requires_grad for t in tensors]
+        ctx.cache: List = []
+        with torch.no_grad():
+            if save_attention:
+                with attn_tcgen05.attention_cache(ctx.cache, "record"):
+                    outs = run_fn(*tensors, *extra)
+            else:
+                outs = run_fn(*tensors, *extra)
+        ctx.save_attention = save_attention
+        ctx.save_for_backward(*tensors)
+        return outs
+
+    @staticmethod
+    def backward(ctx, *grads):
+        tensors = [t.detach().requires_grad_(r) for t, r in zip(ctx.saved_tensors, ctx.requires)]
+        with torch.enable_grad():
+            if ctx.save_attention:
+                with attn_tcgen05.attention_cache(ctx.cache, "replay"):
+                    outs = ctx.run_fn(*tensors, *ctx.extra)
+            else:
+                outs = ctx.run_fn(*tensors, *ctx.extra)
+        if isinstance(outs, torch.Tensor):
+            outs = (outs,)
+        pairs = [(o, g) for o, g in zip(outs, grads) if o.requires_grad and g is not None]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        ctx.cache = []
+        return (None, None, None) + tuple(t.grad if r else None for t, r in zip(tensors, ctx.requires)) + (None,) * len(ctx.extra)
+
+
+def checkpoint_block(run_fn: Callable, tensors, extra=(), save_attention: bool = False):
+    """Run ``run_fn(*tensors, *extra)`` without storing its activations; recompute them in backward.
+    ``tensors`` are differentiable inputs (parameters used inside ``run_fn`` receive gradients as usual);
+    ``extra`` are non-tensor arguments passed through."""
+    return _CheckpointBlock.apply(run_fn, save_attention, len(tensors), *tensors, *extra)

@@ -207,3 +207,30 @@ def test_block_cuda_matches_torch():
         if r > 0.08:
             bad.append((n, r))
     assert not bad, bad[:10]
+
+
+def test_recompute_with_saved_attention_matches_plain_recompute():
+    """The block checkpoint that replays attention from the saved (out, lse) gives the same loss and gradients."""
+    from teletron_b200 import ops
+    from teletron_b200.models.hunyuanvideo import FlowConfig, HunyuanPipeline, hunyuan_13b
+    from teletron_b200.ops import attention_backend
+    from teletron_b200.parallel import state as ps
+    ps.destroy_model_parallel()
+    dev = _dev()
+    g = torch.Generator().manual_seed(0)
+    batch = {"latents": torch.randn(1, 16, 2, 16, 16, generator=g), "prompt_embeds": torch.randn(1, 24, 4096, generator=g),
+             "clip_text_embed": torch.randn(1, 768, generator=g)}
+    out = {}
+    with ops.impl("cuda"):
+        for save in (False, True):
+            cfg = hunyuan_13b(in_channels=16, num_layers=1, num_single_layers=1, recompute_granularity="full",
+                              recompute_save_attention=save)
+            pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"), device=dev, dtype=torch.bfloat16)
+            before = attention_backend.COUNTERS["tcgen05"]
+            loss = pipe(batch)[0]
+            loss.backward()
+            out[save] = (float(loss.detach()), torch.cat([p.grad.float().reshape(-1) for p in pipe.transformer.parameters()
+                                                         if p.grad is not None]),
+                         attention_backend.COUNTERS["tcgen05"] - before)
+    assert out[True][0] == out[False][0]
+    assert _rel(out[True][1], out[False][1]) < 1e-3
