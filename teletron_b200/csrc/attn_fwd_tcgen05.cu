@@ -48,6 +48,12 @@ struct AttnParams {
     int H;                // heads (for the output layout)
     float scale_log2;     // softmax scale * log2(e)
     int* status;
+    // Ulysses head -> sequence all-to-all fused into the epilogue (batch 1): besides the local copy, every output row
+    // is stored into the gathered buffer [text_len + s_local, dest_ld] of the rank that owns that token (text rows,
+    // which come first in the sequence, go to every rank), at this rank's head columns.
+    int push, n_peers, my_rank, text_len, s_local;
+    long dest_ld;
+    __nv_bfloat16* peer_out[TT_MAX_PEERS];
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -273,6 +279,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float inv = 1.f / l;
         const int b = bh / p.H, head = bh - b * p.H;
         __nv_bfloat16* orow = p.out + ((long)b * p.S + row) * ((long)p.H * D) + head * D;
+        // remote destinations of this row (none, the token's owner, or everybody for a text row)
+        int first_dst = 0, n_dst = 0;
+        long drow = 0;
+        if (p.push && row < p.S) {
+            if (row < p.text_len) {
+                n_dst = p.n_peers;
+                drow = row;
+            } else {
+                const int v = row - p.text_len;
+                first_dst = v / p.s_local;
+                n_dst = first_dst < p.n_peers ? 1 : 0;
+                drow = p.text_len + (v - first_dst * p.s_local);
+            }
+        }
+        const long dcol = ((long)p.my_rank * p.H + head) * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
             uint32_t r[32];
@@ -284,7 +305,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     float o[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[g * 8 + i]) * inv;
-                    tt::st8(orow + c * 32 + g * 8, tt::pack8(o));
+                    const tt::bf16x8 pk = tt::pack8(o);
+                    tt::st8(orow + c * 32 + g * 8, pk);
+                    for (int d = 0; d < n_dst; ++d)
+                        tt::st8(p.peer_out[first_dst + d] + drow * p.dest_ld + dcol + c * 32 + g * 8, pk);
                 }
             }
         }
@@ -307,8 +331,31 @@ done:
 }  // namespace
 
 // q, k, v: [BH, S, 128] bf16 contiguous; out [B, S, H*128] bf16; lse [BH, lse_pitch] fp32 (rows < S written).
+static int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
+                           int kv_len, int lse_pitch, float scale, int* status, void* stream, void* const* peer_out,
+                           int n_peers, int my_rank, int text_len, int s_local, long dest_ld);
+
 extern "C" int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
                            int kv_len, int lse_pitch, float scale, int* status, void* stream) {
+    return attn_fwd_launch(q, k, v, out, lse, B, H, S, kv_len, lse_pitch, scale, status, stream, nullptr, 0, 0, 0, 0, 0);
+}
+
+// Forward with the Ulysses head -> sequence all-to-all fused into the epilogue (batch 1).  The sequence is
+// [text_len text tokens | n_peers * s_local video tokens]; peer_out[r] is rank r's gathered buffer
+// [text_len + s_local, dest_ld] (dest_ld = n_peers * H * 128) and receives this rank's H heads at columns
+// [my_rank * H * 128, (my_rank + 1) * H * 128).  `out` still receives the local head-sharded copy for the backward.
+extern "C" int tt_attn_fwd_push(const void* q, const void* k, const void* v, void* out, float* lse, int H, int S,
+                                int kv_len, int lse_pitch, float scale, int* status, void* stream, void* const* peer_out,
+                                int n_peers, int my_rank, int text_len, int s_local, long dest_ld) {
+    if (peer_out == nullptr || n_peers < 1 || n_peers > TT_MAX_PEERS || my_rank < 0 || my_rank >= n_peers) return TT_ERR_ARG;
+    if (text_len < 0 || s_local <= 0 || text_len + (long)n_peers * s_local != S || (dest_ld & 7)) return TT_ERR_ARG;
+    return attn_fwd_launch(q, k, v, out, lse, 1, H, S, kv_len, lse_pitch, scale, status, stream, peer_out, n_peers, my_rank,
+                           text_len, s_local, dest_ld);
+}
+
+static int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
+                           int kv_len, int lse_pitch, float scale, int* status, void* stream, void* const* peer_out,
+                           int n_peers, int my_rank, int text_len, int s_local, long dest_ld) {
     if (B <= 0 || H <= 0 || S <= 0 || kv_len <= 0 || kv_len > S || lse_pitch < S || status == nullptr) return TT_ERR_ARG;
     CUtensorMap tq, tk, tv;
     int rc;
@@ -331,6 +378,13 @@ extern "C" int tt_attn_fwd(const void* q, const void* k, const void* v, void* ou
     p.H = H;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
+    p.push = peer_out != nullptr ? 1 : 0;
+    p.n_peers = n_peers;
+    p.my_rank = my_rank;
+    p.text_len = text_len;
+    p.s_local = s_local;
+    p.dest_ld = dest_ld;
+    for (int r = 0; r < TT_MAX_PEERS; ++r) p.peer_out[r] = (peer_out != nullptr && r < n_peers) ? (__nv_bfloat16*)peer_out[r] : nullptr;
     dim3 grid((S + 2 * BQ - 1) / (2 * BQ), (unsigned)BH);
     attn_fwd_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(tq, tk, tv, p);
     TT_CHECK_LAUNCH();

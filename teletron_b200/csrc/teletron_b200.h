@@ -79,6 +79,9 @@ int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias, const void
  *      lse, delta [B*H, pitch] fp32, pitch % 64 == 0, lse = +inf and delta = 0 at positions >= S ---- */
 int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int kv_len,
                 int lse_pitch, float scale, int* status, void* stream);
+int tt_attn_fwd_push(const void* q, const void* k, const void* v, void* out, float* lse, int H, int S, int kv_len,
+                     int lse_pitch, float scale, int* status, void* stream, void* const* peer_out, int n_peers, int my_rank,
+                     int text_len, int s_local, long dest_ld);
 int tt_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
                 float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len, int pitch, float scale,
                 int* status, void* stream);

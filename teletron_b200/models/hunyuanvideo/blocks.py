@@ -274,15 +274,16 @@ class JointAttention(nn.Module):
                                    self.k_layernorm.weight, cos, sin, ctx, self.added_linear_qkv.weight,
                                    self.added_linear_qkv.bias, self.added_q_layernorm.weight,
                                    self.added_k_layernorm.weight, self.eps)
-        o = ops.attention(q, k, v, kv_valid_len=_fused_kv_len(ws, pad, kv_valid_len))
-        return ("fused", ws, o), None
+        return ("fused", ws, (q, k, v), _fused_kv_len(ws, pad, kv_valid_len)), None
 
     def project_fused(self, handle):
+        """Attention (its epilogue does the head->seq all-to-all) followed by the two output projections."""
         from ...ops import fused_comm as FC
-        _, ws, o = handle
+        _, ws, (q, k, v), kv_len = handle
         tp = self.linear_proj.tp
-        y, yt = FC.fused_a2a_linear(ws, o, self.linear_proj.weight, self.linear_proj.bias if tp == 1 else None,
-                                    self.added_linear_proj.weight, self.added_linear_proj.bias if tp == 1 else None)
+        y, yt = FC.fused_attention_outproj(ws, q, k, v, self.linear_proj.weight, self.linear_proj.bias if tp == 1 else None,
+                                           self.added_linear_proj.weight, self.added_linear_proj.bias if tp == 1 else None,
+                                           kv_len=kv_len)
         if tp > 1:
             g = ps.get_tensor_model_parallel_group()
             y = M.reduce_from_tensor_model_parallel_region(y, g) + self.linear_proj.bias
@@ -394,10 +395,10 @@ class HunyuanSingleDiTLayer(nn.Module):
         w, b = sa.linear_qkv.weight, sa.linear_qkv.bias
         q, k, v = FC.fused_qkv_a2a(ws, xv, w, b, sa.q_layernorm.weight, sa.k_layernorm.weight, cos, sin,
                                    xt, w, b, sa.q_layernorm.weight, sa.k_layernorm.weight, sa.eps)
-        o = ops.attention(q, k, v, kv_valid_len=_fused_kv_len(ws, pad, kv_valid_len))
         tp = self.proj_out.tp
         wo, bo = self.proj_out.weight, (self.proj_out.bias if tp == 1 else None)
-        y, yt = FC.fused_a2a_linear(ws, o, wo, bo, wo, bo, extra=mlp[:, :s], extra_t=mlp[:, s:])
+        y, yt = FC.fused_attention_outproj(ws, q, k, v, wo, bo, wo, bo, extra=mlp[:, :s], extra_t=mlp[:, s:],
+                                           kv_len=_fused_kv_len(ws, pad, kv_valid_len))
         proj = torch.cat([y, yt], dim=1)
         if tp > 1:
             proj = M.reduce_from_tensor_model_parallel_region(proj, ps.get_tensor_model_parallel_group()) + self.proj_out.bias

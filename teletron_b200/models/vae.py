@@ -227,9 +227,10 @@ class AutoencoderKLHunyuanVideo(nn.Module):
     def _tiled(self, x, fn, tile: int, ratio_in_out: float):
         """Apply ``fn`` on overlapping spatial tiles of ``x`` and blend the seams (sizes in ``x`` pixels)."""
         B, C, T, H, W = x.shape
-        stride = int(tile * (1 - self.tile_overlap))
-        blend = int((tile - stride) * ratio_in_out)
-        keep = int(stride * ratio_in_out)
+        align = max(1, int(round(1.0 / ratio_in_out)))                 # keep tile strides on latent-pixel boundaries
+        stride = max(align, int(tile * (1 - self.tile_overlap)) // align * align)
+        blend = int(round((tile - stride) * ratio_in_out))
+        keep = int(round(stride * ratio_in_out))
         rows = []
         for i in range(0, H, stride):
             row = []

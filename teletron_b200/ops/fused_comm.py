@@ -56,10 +56,12 @@ class UlyssesWorkspace:
         self.text_off = 0
         self.video_off = text_len
         n_qkv = self.h_loc * self.S_tot * 128 * 2                  # bytes of one of q / k / v (batch 1)
-        total = 8 * (n_qkv + 1024)
+        n_g = (text_len + s_local) * heads * 128 * 2               # gathered attention output: my tokens, all heads
+        total = 8 * (n_qkv + 1024) + n_g + 1024
         self.heap = heap or SymmetricHeap(group, total, device)
         names = ("q", "k", "v", "o", "dq", "dk", "dv", "do")
         self.off = {n: self.heap.alloc(n_qkv) for n in names}
+        self.off["g"] = self.heap.alloc(n_g)
 
     def head_major(self, name: str, rank: Optional[int] = None) -> torch.Tensor:
         return self.heap.tensor(self.off[name], (1, self.h_loc, self.S_tot, 128), BF16, rank)
@@ -235,6 +237,117 @@ def fused_a2a_linear(ws: UlyssesWorkspace, o, w, b, wt, bt, extra=None, extra_t=
     """``o [1, S_tot, heads/cp * 128]`` (this rank's heads, all tokens) -> projections of this rank's video tokens
     (weights ``w``) and of the replicated text tokens (weights ``wt``)."""
     return _FusedAllToAllLinear.apply(ws, o, w, b, wt, bt, extra, extra_t)
+
+
+# ---------------------------------------------------------------------------------------------
+# F2 (push form): attention whose epilogue performs the head -> sequence all-to-all, then local projections
+# ---------------------------------------------------------------------------------------------
+
+def _local_gemm_extra(ws: UlyssesWorkspace, a_rows: torch.Tensor, extra, w, bias):
+    """``[a_rows | extra] @ w^T + bias`` without materialising the concatenation (the K loop switches source)."""
+    M, G = a_rows.shape
+    N, K = w.shape
+    if extra is None:
+        return gemm.gemm_nt(a_rows, w, bias)
+    out = torch.empty(M, N, dtype=BF16, device=w.device)
+    call("tt_gemm_comm_bf16", _table([a_rows.data_ptr()]), c_int(1), c_int(1), c_long(M), c_int(G), c_int(0), ptr(extra),
+         c_long(extra.stride(0)), ptr(w), c_int(0), c_long(w.stride(0)), ptr(out), c_long(N), ptr(bias), c_int(M), c_int(N),
+         c_int(K), c_int(0), c_int(0), c_int(0), None, c_int(0), c_int(0), c_long(0), ptr(status_tensor(w.device)), stream())
+    return out
+
+
+class _FusedAttentionOutProj(torch.autograd.Function):
+    """Attention over this rank's heads with the head -> sequence all-to-all done by the attention epilogue (every
+    output row is stored straight into the gathered buffer of the rank that owns the token, crossing NVLink once),
+    followed by the local output projections of the video and the text stream."""
+
+    @staticmethod
+    def forward(ctx, ws, kv_len, scale, q, k, v, w, b, wt, bt, extra, extra_t):
+        from . import attn_tcgen05 as A
+        import math
+        H_all = ws.heads
+        T, s = ws.T, ws.s
+        sc = (1.0 / math.sqrt(128)) if scale is None else float(scale)
+        kvl = ws.S_tot if kv_len is None else int(kv_len)
+        q, k, v = (check(t.contiguous(), BF16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+        g = ws.heap.tensor(ws.off["g"], (T + s, H_all * 128), BF16)
+        ws.heap.barrier()                  # peers are done with the previous gathered buffer / o
+        cached = A._CACHE.pop(0) if (A._CACHE_MODE == "replay" and A._CACHE) else None
+        if cached is None:
+            out = torch.empty(1, ws.S_tot, ws.h_loc * 128, dtype=BF16, device=q.device)
+            pitch = (ws.S_tot + 63) // 64 * 64
+            lse = torch.full((1, ws.h_loc, pitch), float("inf"), dtype=torch.float32, device=q.device)
+            call("tt_attn_fwd_push", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(ws.h_loc), c_int(ws.S_tot), c_int(kvl),
+                 c_int(pitch), c_float(sc), ptr(status_tensor(q.device)), stream(), ws.table("g"), c_int(ws.cp),
+                 c_int(ws.rank), c_int(T), c_int(s), c_long(H_all * 128))
+            if A._CACHE_MODE == "record":
+                A._CACHE.append((out, lse))
+            ws.heap.barrier()              # every rank's rows have landed
+        else:
+            # recompute pass with the attention output kept: redo only the all-to-all (peer-reading copy)
+            out, lse = cached
+            ws.token_major("o").copy_(out)
+            ws.heap.barrier()
+            span = ws.h_loc * 128
+            call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(T), c_int(span), c_long(ws.text_off), ptr(g[:T]), stream())
+            call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(s), c_int(span), c_long(ws.video_off + ws.rank * s),
+                 ptr(g[T:]), stream())
+        ex = None if extra is None else check(extra.reshape(s, -1).contiguous(), BF16, "extra")
+        ext = None if extra_t is None else check(extra_t.reshape(T, -1).contiguous(), BF16, "extra_t")
+        y = _local_gemm_extra(ws, g[T:], ex, w, b)
+        yt = _local_gemm_extra(ws, g[:T], ext, wt, bt)
+        ctx.ws, ctx.sc, ctx.kvl = ws, sc, kvl
+        ctx.save_for_backward(q, k, v, out, lse, w, wt, ex, ext, g)
+        ctx.has = (b is not None, bt is not None)
+        ctx.extra_shapes = (None if extra is None else extra.shape, None if extra_t is None else extra_t.shape)
+        return y.view(1, s, -1), yt.view(1, T, -1)
+
+    @staticmethod
+    def backward(ctx, dy, dyt):
+        from . import attn_backward
+        ws: UlyssesWorkspace = ctx.ws
+        q, k, v, out, lse, w, wt, ex, ext, g = ctx.saved_tensors
+        T, s = ws.T, ws.s
+        span = ws.h_loc * 128
+        G = ws.cp * span
+        K = w.shape[1]
+        dev = q.device
+        dy2 = check(dy.reshape(s, -1).contiguous(), BF16, "dy")
+        dyt2 = check(dyt.reshape(T, -1).contiguous(), BF16, "dyt")
+        # weight gradients: the gathered activations are local
+        dw = torch.empty_like(w)
+        gemm.gemm_tn_into(dy2, g[T:], dw[:, :G])
+        dwt_same = wt.data_ptr() == w.data_ptr()
+        dwt = torch.empty_like(wt)
+        gemm.gemm_tn_into(dyt2, g[:T], dwt[:, :G])
+        if ex is not None:
+            gemm.gemm_tn_into(dy2, ex, dw[:, G:])
+        if ext is not None:
+            gemm.gemm_tn_into(dyt2, ext, dwt[:, G:])
+        db = dy2.sum(0, dtype=torch.float32).to(BF16) if ctx.has[0] else None
+        dbt = dyt2.sum(0, dtype=torch.float32).to(BF16) if ctx.has[1] else None
+        # data gradient of the video rows: every head's columns are pushed to the head's owner by the GEMM epilogue
+        dex = torch.empty(s, K - G, dtype=BF16, device=dev) if ex is not None else None
+        ws.heap.barrier()                  # peers are done reading the previous contents of `do`
+        call("tt_gemm_comm_bf16", _table([dy2.data_ptr()]), c_int(ws.cp), c_int(0), c_long(s), c_int(0), c_int(0), None,
+             c_long(0), ptr(w), c_int(1), c_long(w.stride(0)), ptr(dex), c_long(0 if dex is None else dex.stride(0)), None,
+             c_int(s), c_int(K), c_int(w.shape[0]), c_int(0), c_int(ws.rank), c_int(1), ws.table("do"), c_int(span),
+             c_int(ws.video_off + ws.rank * s), c_long(span), ptr(status_tensor(dev)), stream())
+        # text rows are replicated: keep this rank's heads, scaled by cp
+        dot_full = gemm.gemm_nn(dyt2, wt)
+        do_local = ws.token_major("do")
+        do_local[0, ws.text_off:ws.text_off + T, :].copy_(dot_full[:, ws.rank * span:(ws.rank + 1) * span] * float(ws.cp))
+        dext = dot_full[:, G:].contiguous().view(ctx.extra_shapes[1]) if ext is not None else None
+        ws.heap.barrier()                  # all pushed gradient tiles have landed
+        dq, dk, dv = attn_backward.backward(do_local, q, k, v, out, lse, ctx.sc, ctx.kvl)
+        del dwt_same
+        return (None, None, None, dq, dk, dv, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
+
+
+def fused_attention_outproj(ws: UlyssesWorkspace, q, k, v, w, b, wt, bt, extra=None, extra_t=None, kv_len=None, scale=None):
+    """``q, k, v [1, heads/cp, T + cp*s, 128]`` -> (projection of this rank's video tokens with ``w``, projection of the
+    text tokens with ``wt``); ``extra`` / ``extra_t`` are local tensors concatenated to the attention output along K."""
+    return _FusedAttentionOutProj.apply(ws, kv_len, scale, q, k, v, w, b, wt, bt, extra, extra_t)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -68,3 +68,16 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         return out
     COUNTERS["cublas"] += 1
     return torch.matmul(a.t(), b)
+
+
+def gemm_tn_into(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[:] = a.T @ b`` where ``out`` may be a column slice of a larger row-major matrix."""
+    if _BACKEND != "cublas":
+        from . import gemm_tcgen05
+        if gemm_tcgen05.supported(a, b, "tn") and out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+            COUNTERS["tcgen05"] += 1
+            gemm_tcgen05.gemm(a, b, "tn", out=out)
+            return out
+    COUNTERS["cublas"] += 1
+    out.copy_(torch.matmul(a.t(), b))
+    return out

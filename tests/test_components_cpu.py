@@ -1,0 +1,268 @@
+"""CPU tests of the framework components around the model: ops oracle identities, parallel-state layout, optimizer
+(ZeRO-1 sharding, split16 master weights), data pipeline, VAE, text encoders, watchdog / heartbeat."""
+
+import math
+import os
+import time
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+# ---------------------------------------------------------------- ops oracle
+def test_rope_matches_complex_rotation():
+    from teletron_b200.ops import reference as R
+    x = torch.randn(2, 3, 10, 16)
+    ang = torch.rand(10, 8) * 6.28
+    cos, sin = ang.cos().repeat_interleave(2, 1), ang.sin().repeat_interleave(2, 1)
+    y = R.apply_rope(x, cos, sin)
+    xc = torch.view_as_complex(x.reshape(2, 3, 10, 8, 2))
+    ref = torch.view_as_real(xc * torch.polar(torch.ones_like(ang), ang)).reshape(2, 3, 10, 16)
+    torch.testing.assert_close(y, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_layernorm_modulate_and_fused_variant():
+    from teletron_b200.ops import reference as R
+    x, br = torch.randn(2, 7, 32), torch.randn(2, 7, 32)
+    g, sc, sh = torch.randn(2, 32), torch.randn(2, 32), torch.randn(2, 32)
+    y = R.layernorm_modulate(x, sc, sh)
+    ref = torch.nn.functional.layer_norm(x, (32,), eps=1e-6) * (1 + sc[:, None]) + sh[:, None]
+    torch.testing.assert_close(y, ref, rtol=1e-5, atol=1e-5)
+    nr, y2 = R.gate_residual_layernorm_modulate(x, br, g, sc, sh)
+    torch.testing.assert_close(nr, x + g[:, None] * br)
+    torch.testing.assert_close(y2, R.layernorm_modulate(nr, sc, sh))
+
+
+def test_qkv_projection_layout_and_joint():
+    from teletron_b200.ops import reference as R
+    H, D, heads = 64, 16, 4
+    x, xt = torch.randn(1, 6, H), torch.randn(1, 3, H)
+    w, b = torch.randn(3 * H, H) * 0.1, torch.randn(3 * H)
+    qw, kw = torch.rand(D) + 0.5, torch.rand(D) + 0.5
+    ang = torch.rand(6, D // 2)
+    cos, sin = ang.cos().repeat_interleave(2, 1), ang.sin().repeat_interleave(2, 1)
+    q, k, v = R.qkv_projection(x, w, b, qw, kw, cos, sin, heads)
+    raw = (x @ w.t() + b).view(1, 6, heads, 3, D)
+    torch.testing.assert_close(v, raw[:, :, :, 2].transpose(1, 2))
+    torch.testing.assert_close(q, R.apply_rope(R.rmsnorm(raw[:, :, :, 0].transpose(1, 2), qw), cos, sin))
+    jq, jk, jv = R.joint_qkv_projection(x, w, b, qw, kw, cos, sin, xt, w, b, qw, kw, heads)
+    assert jq.shape == (1, heads, 9, D)
+    torch.testing.assert_close(jq[:, :, :6], q)
+
+
+def test_flow_scheduler_and_weighting():
+    from teletron_b200.models.hunyuanvideo.pipeline import FlowMatchScheduler, compute_loss_weighting
+    s = FlowMatchScheduler(1000, 1.0)
+    assert abs(float(s.sigmas[0]) - 1.0) < 1e-6 and abs(float(s.sigmas[-1]) - 0.001) < 1e-6
+    s7 = FlowMatchScheduler(1000, 7.0)
+    x = s.sigmas
+    torch.testing.assert_close(s7.sigmas, 7 * x / (1 + 6 * x))
+    w = compute_loss_weighting("cosmap", torch.tensor([0.5]))
+    assert abs(float(w) - 2 / (math.pi * 0.5)) < 1e-6
+
+
+# ---------------------------------------------------------------- parallel state
+def test_rank_lists_follow_tp_cp_dp_order():
+    from teletron_b200.parallel.state import build_comm_pairs, build_rank_lists, rank_coords
+    L = build_rank_lists(8, 2, 2)
+    assert L["tp"] == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert L["cp"] == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert L["dp"] == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert L["dp_cp"] == [[0, 2, 4, 6], [1, 3, 5, 7]]
+    assert L["tp_cp"] == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert rank_coords(6, 2, 2) == {"tp": 0, "cp": 1, "dp": 1}
+    pairs = build_comm_pairs(6, 2, 2, 3)            # 6 DiT ranks (tp2 cp3 -> dp1) + 2 encoder ranks
+    assert [(p.producer, p.consumer) for p in pairs] == [(6, 0)]
+    pairs = build_comm_pairs(8, 2, 1, 2)            # dp 4, two producers
+    assert [(p.producer, p.consumer, p.dp_rank) for p in pairs] == [(8, 0, 0), (9, 2, 1), (8, 4, 2), (9, 6, 3)]
+    with pytest.raises(ValueError):
+        build_rank_lists(6, 4, 1)
+
+
+def _groups(rank, world):
+    import torch.distributed as dist
+    from teletron_b200.parallel import state as ps
+    ps.initialize_model_parallel(2, 1, encoder_world_size=1)      # 3 ranks: tp group [0,1] + encoder rank 2
+    info = (ps.is_dit_rank(), ps.get_tensor_model_parallel_world_size(), ps.get_tensor_model_parallel_rank(),
+            ps.get_tensor_context_parallel_src_rank(), [(p.producer, p.consumer) for p in ps.get_comm_pairs()])
+    if ps.is_dit_rank():
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t, group=ps.get_tensor_model_parallel_group())
+        assert float(t) == 3.0
+    return info
+
+
+def test_every_rank_walks_the_same_group_list_with_encoder_ranks():
+    res = run_distributed(_groups, 3)
+    assert res[0][0] and res[1][0] and not res[2][0]
+    assert res[0][4] == [(2, 0)]
+
+
+# ---------------------------------------------------------------- optimizer
+def test_split16_pack_is_exact():
+    from teletron_b200.ops.optim import _pack16, _unpack16
+    w = torch.randn(10000) * torch.logspace(-6, 3, 10000)
+    hi, lo = _pack16(w)
+    assert torch.equal(_unpack16(hi, lo).view(torch.int32), w.view(torch.int32))
+    assert (hi.float() - w).abs().max() <= (w.abs().max() * 2 ** -8)
+
+
+def _zero1(rank, world, master_mode):
+    import torch.distributed as dist
+    from teletron_b200.parallel.grad_buffer import DistributedDataParallel
+    from teletron_b200.training.optimizer import DistributedOptimizer
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.GELU(), torch.nn.Linear(40, 8))
+    ref = torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.GELU(), torch.nn.Linear(40, 8))
+    ref.load_state_dict(net.state_dict())
+    ddp = DistributedDataParallel(net, dist.group.WORLD, use_distributed_optimizer=True, bucket_bytes=1024)
+    opt = DistributedOptimizer(ddp, lr=1e-2, weight_decay=0.1, clip_grad=1.0, master_mode=master_mode)
+    decay = [p for n, p in ref.named_parameters() if not n.endswith("bias")]
+    nodecay = [p for n, p in ref.named_parameters() if n.endswith("bias")]
+    ropt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": nodecay, "weight_decay": 0.0}], lr=1e-2)
+    for step in range(4):
+        g = torch.Generator().manual_seed(step)
+        xs = torch.randn(world, 5, 24, generator=g)
+        opt.zero_grad()
+        net(xs[rank]).pow(2).mean().backward()
+        ddp.finish_grad_sync()
+        opt.step()
+        ropt.zero_grad()
+        sum(ref(xs[r]).pow(2).mean() for r in range(world)).div(world).backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        ropt.step()
+    return [(a.detach() - b.detach()).abs().max().item() for a, b in zip(net.parameters(), ref.parameters())]
+
+
+@pytest.mark.parametrize("master_mode", ["fp32", "none"])
+def test_zero1_adamw_matches_torch_adamw(master_mode):
+    for diffs in run_distributed(_zero1, 2, master_mode):
+        assert max(diffs) < 2e-5, diffs
+
+
+def test_lr_schedule():
+    from teletron_b200.training.optimizer import OptimizerParamScheduler
+
+    class O:
+        lr = 0.0
+    o = O()
+    s = OptimizerParamScheduler(o, max_lr=1.0, min_lr=0.1, lr_warmup_steps=10, lr_decay_steps=110, lr_decay_style="cosine")
+    s.step(5)
+    assert abs(o.lr - 0.5) < 1e-9
+    s.step(5)
+    assert abs(o.lr - 1.0) < 1e-9
+    s.step(50)
+    assert abs(o.lr - 0.55) < 1e-6
+    s.step(100)
+    assert abs(o.lr - 0.1) < 1e-9
+
+
+# ---------------------------------------------------------------- data
+def test_fake_dataset_shapes_and_determinism():
+    from teletron_b200.data import build_dataset
+    ds = build_dataset("FakeDataset", num_frames=9, video_resolution=(64, 32), text_len=120)
+    a, b = ds[3], ds[3]
+    assert a["images"].shape == (9, 3, 32, 64) and a["latents"].shape == (16, 3, 4, 8)
+    assert a["prompt_embeds"].shape == (120, 4096) and a["clip_text_embed"].shape == (768,) and len(a["prompt"]) == 880
+    assert torch.equal(a["latents"], b["latents"]) and a["prompt"] == b["prompt"]
+    assert not torch.equal(ds[4]["latents"], a["latents"])
+
+
+def test_samplers_partition_global_batches():
+    from teletron_b200.data.samplers import PretrainingRandomSampler, PretrainingSampler
+    got = [list(PretrainingSampler(20, 4, 2, r, 2)) for r in range(2)]
+    assert got[0][0] == [4, 5] and got[1][0] == [6, 7] and got[0][1] == [8, 9]
+    seen = set()
+    for r in range(2):
+        for b in PretrainingRandomSampler(16, 0, 2, r, 2, seed=1):
+            seen.update(b)
+    assert seen == set(range(16))
+
+
+def test_koala_dataset_reads_tensor_clips(tmp_path):
+    from teletron_b200.data import build_dataset
+    clip = torch.randint(0, 255, (20, 40, 48, 3), dtype=torch.uint8)
+    torch.save(clip, tmp_path / "a.pt")
+    pe = str(torch.zeros(2, 4).tolist())
+    ce = str(torch.zeros(4).tolist())
+    lat = str(torch.zeros(1, 2, 3, 2, 2).tolist())
+    (tmp_path / "list.txt").write_text(f"a.pt;a prompt;{pe};{ce};{lat}\n")
+    opt = {"phase": "test", "anno_file": str(tmp_path / "list.txt"), "data_prefix": str(tmp_path),
+           "sample_types": {"fragments": {"fragments_h": 1, "fragments_w": 1, "fsize_h": 32, "fsize_w": 32, "aligned": 1,
+                                          "clip_len": 5, "frame_interval": 1, "num_clips": 1}}}
+    ds = build_dataset("KoalaDataset", opt=opt, num_frames=9, video_resolution=(32, 16))
+    item = ds[0]
+    assert item["images"].shape == (9, 3, 16, 32) and item["first_ref_image"].shape == (3, 16, 32)
+    assert item["prompt"] == "a prompt" and item["latents"].shape == (2, 3, 2, 2)
+
+
+# ---------------------------------------------------------------- models around the DiT
+def test_vae_shapes_tiling_and_roundtrip_geometry():
+    from teletron_b200.models.vae import AutoencoderKLHunyuanVideo
+    torch.manual_seed(0)
+    vae = AutoencoderKLHunyuanVideo(block_out_channels=(32, 32, 64, 64)).eval()
+    x = torch.rand(1, 3, 9, 64, 96) * 2 - 1
+    with torch.no_grad():
+        z = vae.encode(x, sample=False)
+        assert z.shape == (1, 16, 3, 8, 12)
+        y = vae.decode(z)
+        assert y.shape == x.shape
+        # the convolutions are causal in time: output frame t sees input frames <= t only
+        from teletron_b200.models.vae import CausalConv3d
+        conv = CausalConv3d(3, 4, 3)
+        x2 = x.clone()
+        x2[:, :, 4:] = 0
+        torch.testing.assert_close(conv(x2)[:, :, :4], conv(x)[:, :, :4])
+        vae.tile_sample_min = 48
+        vae.enable_tiling(True)
+        zt = vae.encode(x, sample=False)
+        assert zt.shape == z.shape
+
+
+def test_text_encoders_from_config():
+    from teletron_b200.models.text_encoders import (ClipTextEncoder, LlamaTextEncoder, clip_text_config, llama_config,
+                                                    pad_prompt, truncate_prompt)
+    llama = LlamaTextEncoder(max_length=16, dtype=torch.float32, config=llama_config(2, 64, 4, 2, 128, 1000))
+    emb, mask = llama(["a short prompt", "another slightly longer prompt here"])
+    assert emb.shape == (2, 16, 64) and mask.sum(1).tolist() == [4, 6]
+    clip = ClipTextEncoder(max_length=12, dtype=torch.float32, config=clip_text_config(2, 32, 4, 500, 12))
+    assert clip(["x y z"]).shape == (1, 32)
+    t = truncate_prompt(emb[:1], mask[:1])
+    assert t.shape == (4, 64)
+    p, m = pad_prompt(t, 10)
+    assert p.shape == (10, 64) and m.sum() == 4
+
+
+# ---------------------------------------------------------------- failure detection (host side only)
+def test_step_watchdog_fires_without_heartbeat():
+    from teletron_b200.training.watchdog import StepWatchdog
+    fired = []
+    w = StepWatchdog(0.2, on_timeout=lambda step, idle: fired.append((step, idle)), poll=0.05)
+    w.beat(7)
+    time.sleep(0.6)
+    w.stop()
+    assert fired and fired[0][0] == 7
+    ok = StepWatchdog(0.5, on_timeout=lambda s, i: fired.append("bad"), poll=0.05)
+    for i in range(5):
+        ok.beat(i)
+        time.sleep(0.05)
+    ok.stop()
+    assert "bad" not in fired
+
+
+def test_heartbeat_reports_departed_and_silent_ranks():
+    import torch.distributed as dist
+    from teletron_b200.training.watchdog import Heartbeat
+    store = dist.HashStore()
+    hb = [Heartbeat(store, r, 3, timeout=0.2) for r in range(3)]
+    assert hb[0].dead_ranks() == []
+    hb[1].leave()
+    assert hb[0].dead_ranks() == [1]
+    time.sleep(0.3)
+    hb[0].dead_ranks()
+    time.sleep(0.3)
+    assert hb[0].dead_ranks() == [1, 2]        # rank 2 stopped beating
+    hb[2].beat()
+    assert hb[0].dead_ranks() == [1]
