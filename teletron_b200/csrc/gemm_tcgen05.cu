@@ -270,12 +270,13 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                         for (int j = 0; j < 8; ++j) v[c * 32 + g * 8 + j] = __uint_as_float(r[g * 8 + j]) + bv[j];
                     }
                 }
-                if (row_ok && (!p.only_local || dest == p.my_rank)) {
-                    if (p.aux != nullptr) {
-                        __nv_bfloat16* arow = p.aux + (long)row * p.ldc + n0;
+                // the raw projection is kept for every head (the backward rebuilds all of them, also for replicated tokens)
+                if (row_ok && p.aux != nullptr) {
+                    __nv_bfloat16* arow = p.aux + (long)row * p.ldc + n0;
 #pragma unroll
-                        for (int g = 0; g < 16; ++g) tt::st8(arow + g * 8, tt::pack8(v + g * 8));
-                    }
+                    for (int g = 0; g < 16; ++g) tt::st8(arow + g * 8, tt::pack8(v + g * 8));
+                }
+                if (row_ok && (!p.only_local || dest == p.my_rank)) {
                     const int b = row / p.s_in, srow = row - b * p.s_in;
                     if (which < 2) {
                         float ss = 0.f;

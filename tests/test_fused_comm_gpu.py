@@ -150,12 +150,21 @@ def test_fused_ulysses_model_matches_nccl_path():
         batch = {"latents": torch.randn(1, 16, 3, 30, 34, generator=gen), "prompt_embeds": torch.randn(1, 40, 4096, generator=gen),
                  "clip_text_embed": torch.randn(1, 768, generator=gen)}       # 3*15*17 = 765 video tokens: odd -> padded to 766
         res = {}
-        for fused in (False, True):
+        # poison recycled allocator blocks so that any buffer a kernel leaves partly unwritten shows up as NaN
+        junk = [torch.full((64 << 20,), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(8)]
+        del junk
+        from teletron_b200.parallel.grad_buffer import DistributedDataParallel
+        for fused in (True, False):
             blocks.set_fused_comm(fused)
             pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"), device=torch.device("cuda", rank), dtype=torch.bfloat16)
-            loss = pipe(batch)[0]
-            loss.backward()
+            ddp = DistributedDataParallel(pipe, ps.get_data_parallel_group(with_context_parallel=True))
+            for it in range(2):
+                ddp.zero_grad_buffer()
+                pipe.step = 0
+                loss = pipe(batch)[0]
+                loss.backward()
             res[fused] = (float(loss.detach()), {n: p.grad.float().clone() for n, p in pipe.transformer.named_parameters() if p.grad is not None})
+            assert all(torch.isfinite(g).all() for g in res[fused][1].values()), "non-finite gradient"
         assert abs(res[True][0] - res[False][0]) < 2e-2 * abs(res[False][0]), (res[True][0], res[False][0])
         bad = []
         for n, gref in res[False][1].items():
