@@ -156,6 +156,8 @@ def main():
             "--optimizer-state-dtype", "bf16" if single else "fp32"]
     if not a.no_recompute:
         argv += ["--recompute-granularity", "full", "--recompute-method", "block"]
+    if a.impl == "ours" and a.fused_comm and a.gpus > 1:
+        argv += ["--fused-comm"]
     args = initialize(argv=argv)
     dev = args.device
     rank = args.rank

@@ -58,7 +58,7 @@ class ParamAndGradBuffer:
     """Flat storage for all trainable parameters of one dtype and their gradients."""
 
     def __init__(self, named_params: List[Tuple[str, nn.Parameter]], shard_count: int,
-                 bucket_bytes: int = 512 << 20, grad_dtype: Optional[torch.dtype] = None):
+                 bucket_bytes: int = 512 << 20, grad_dtype: Optional[torch.dtype] = None, storage=None):
         if not named_params:
             raise ValueError("no parameters")
         self.dtype = named_params[0][1].dtype
@@ -89,8 +89,14 @@ class ParamAndGradBuffer:
         # every shard boundary stays 16-byte aligned
         self.numel = _align(off, 8 * shard_count)
         self.regions[-1].end = self.numel
-        self.param_data = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
-        self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+        if storage is None:
+            self.param_data = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+        else:
+            # caller-provided storage (a symmetric heap, so that peers can read gradients and write parameters)
+            self.param_data, self.grad_data = storage(self.numel, self.dtype, self.grad_dtype)
+            self.param_data.zero_()
+            self.grad_data.zero_()
         for _, p in ordered:
             s, e = self.param_index[p]
             view = self.param_data[s:e].view(p.shape)
@@ -146,7 +152,8 @@ class DistributedDataParallel(nn.Module):
 
     def __init__(self, module: nn.Module, group=None, use_distributed_optimizer: bool = True,
                  overlap_grad_reduce: bool = False, bucket_bytes: int = 512 << 20,
-                 grad_dtype: Optional[torch.dtype] = None, check_for_nan_in_grad: bool = False, tp_group=None):
+                 grad_dtype: Optional[torch.dtype] = None, check_for_nan_in_grad: bool = False, tp_group=None,
+                 fused_comm: bool = False):
         super().__init__()
         self.module = module
         self.group = group
@@ -159,7 +166,21 @@ class DistributedDataParallel(nn.Module):
         by_dtype: Dict[torch.dtype, List[Tuple[str, nn.Parameter]]] = {}
         for n, p in named:
             by_dtype.setdefault(p.dtype, []).append((n, p))
-        self.buffers = [ParamAndGradBuffer(v, self.world, bucket_bytes, grad_dtype) for v in by_dtype.values()]
+        self.heap = None
+        self.heap_offsets = None
+        storage = None
+        if fused_comm and self.world > 1 and len(by_dtype) == 1 and named[0][1].is_cuda and named[0][1].dtype == torch.bfloat16:
+            # gradient reduce-scatter and parameter all-gather by in-kernel NVLink loads / stores: both flat
+            # buffers live in a symmetric heap mapped into every data-parallel peer
+            from .symm_mem import SymmetricHeap
+
+            def storage(numel, dtype, grad_dtype):
+                nbytes = numel * 2
+                self.heap = SymmetricHeap(group, 2 * nbytes + 4096)
+                po, go = self.heap.alloc(nbytes), self.heap.alloc(nbytes)
+                self.heap_offsets = (po, go)
+                return self.heap.tensor(po, (numel,), dtype), self.heap.tensor(go, (numel,), grad_dtype)
+        self.buffers = [ParamAndGradBuffer(v, self.world, bucket_bytes, grad_dtype, storage) for v in by_dtype.values()]
         self.grad_scale = 1.0 / self.world
         self._sync_enabled = True
         self._hooks = []
@@ -208,6 +229,13 @@ class DistributedDataParallel(nn.Module):
             raise RuntimeError("non-finite gradient in bucket [%d, %d)" % (b.start, b.end))
         if self.world == 1:
             return
+        if self.heap is not None and self.use_distributed_optimizer:
+            # peers' buckets are read over NVLink and summed in fp32 with the 1/(dp*cp) scale folded in
+            from ..ops import fused_comm as FC
+            s, e = buf.shard_range(b, self.rank)
+            FC.fused_grad_reduce_scatter(self.heap, self.heap_offsets[1], s, e - s, buf.grad_data[s:e], self.grad_scale)
+            b.handle = "fused"
+            return
         g.mul_(self.grad_scale)
         if self.use_distributed_optimizer:
             s, e = buf.shard_range(b, self.rank)
@@ -225,12 +253,16 @@ class DistributedDataParallel(nn.Module):
         """Wait for (or issue) every bucket collective; afterwards each rank's shard holds the
         averaged gradient (ZeRO-1) or the whole buffer does (all-reduce mode)."""
         allreduce_tp_partial_grads(self._tp_partial, self.tp_group)
+        if self.heap is not None:
+            self.heap.barrier()        # every rank's gradients are complete before anyone reads them
         for buf in self.buffers:
             for b in buf.buckets:
                 if b.handle is None:
                     self._launch(buf, b, async_op=False)
                 elif hasattr(b.handle, "wait"):
                     b.handle.wait()
+        if self.heap is not None:
+            self.heap.barrier()        # all peers have read this rank's buckets; they may be overwritten again
         self._reset_pending()
 
     def zero_grad_buffer(self):

@@ -15,7 +15,7 @@ Memory modes (sized for 180 GB of HBM3e):
   2 extra bytes/param.  With ``state_dtype=bf16`` the whole optimizer costs 6 bytes/param, which
   is what lets the full 13B model train on a single B200.
 
-The arithmetic is :func:`teletron_b200.ops.reference.adamw_step_` semantics; on CUDA the update of
+The arithmetic is that of :func:`teletron_b200.ops.optim.adamw_update_reference`; on CUDA the update of
 a shard is one launch of the fused sm_100a kernel (``csrc/optim.cu``).
 """
 
@@ -133,7 +133,13 @@ class DistributedOptimizer:
                         lr=self.lr, beta1=b1, beta2=b2, eps=self.eps,
                         weight_decay=self.weight_decay if r.weight_decay else 0.0,
                         step=self.step_count, grad_scale=clip_coef)
-            if self.sharded:
+            if self.sharded and getattr(self.ddp, "heap", None) is not None:
+                # parameter all-gather by peer stores: every rank writes its updated shard into all replicas
+                from ..ops import fused_comm as FC
+                for st in states:
+                    FC.fused_param_all_gather(self.ddp.heap, self.ddp.heap_offsets[0], st.start, buf.param_data[st.start:st.end])
+                self.ddp.heap.barrier()
+            elif self.sharded:
                 for b, st in zip(buf.buckets, states):
                     dist.all_gather_into_tensor(buf.param_data[b.start:b.end], buf.param_data[st.start:st.end],
                                                 group=self.ddp.group)
