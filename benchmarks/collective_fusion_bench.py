@@ -5,7 +5,9 @@ benchmarks/collective_fusion_bench.py [--tokens 119056] [--iters 10]``.
 
 Paths, each against the unfused NCCL + cuBLAS sequence the reference runs:
   (a) Ulysses seq->head all-to-all fused with the QKV GEMM + QK-RMSNorm + RoPE
-  (b) head->seq all-to-all fused with the output projection
+  (b) head->seq all-to-all fused with the output projection, in two forms: the projection GEMM pulling its A operand
+      per head from the owner rank, and (the form the model uses) the attention epilogue pushing every output row to the
+      token's owner so that the projection is local
   (c) tensor-parallel all-gather->GEMM and GEMM->reduce-scatter on the 3072 x 12288 MLP
 Times are CUDA events on each rank, max over ranks.  The roofline per path is the slower of
 FLOPs / measured bf16 peak and NVLink bytes / 770 GB/s (measured peer copy, per direction per GPU).
@@ -120,6 +122,31 @@ def main():
         roof = max(fl / (pk * 1e12), nbytes / (LINK_GBS * 1e9)) * 1e3
         out["b_a2a_outproj"] = {"fused_ms": tb_f, "nccl_cublas_ms": tb_u, "speedup": tb_u / tb_f, "roofline_ms": roof,
                                 "roofline_fraction": roof / tb_f}
+        # (b') push form used by the model: the attention epilogue performs the head -> sequence all-to-all (every output
+        # row crosses NVLink once, while the tensor core is busy), then the projections are local
+        qh, kh, vh = (ws.head_major(n) for n in ("q", "k", "v"))
+        for t in (qh, kh, vh):
+            t.copy_(rnd(1, ws.h_loc, ws.S_tot, 128))
+        from teletron_b200.ops import attn_tcgen05 as AT
+
+        def fused_bp():
+            with torch.no_grad():
+                FC.fused_attention_outproj(ws, qh, kh, vh, wo, bo, wo, bo)
+
+        def unfused_bp():
+            with torch.no_grad():
+                oo = AT.forward(qh, kh, vh, None, None)[0]
+                ov = oo[:, T:].reshape(1, ws.S, ws.h_loc, 128).transpose(1, 2)
+                ov = M._a2a_seq_to_heads(ov.contiguous(), g).transpose(1, 2).reshape(1, s, H)
+                ot = M._gather(oo[:, :T].contiguous(), g, 2, None)
+                return cuda_ops.linear(ov, wo, bo), cuda_ops.linear(ot, wo, bo)
+        it2 = max(2, a.iters // 4)
+        tp_f, tp_u = timeit(fused_bp, it2), timeit(unfused_bp, it2)
+        fl = 4.0 * ws.S_tot * ws.S_tot * 128 * ws.h_loc + 2.0 * s * H * H
+        nbytes = s * H * 2 * (world - 1) / world
+        roof = max(fl / (pk * 1e12), nbytes / (LINK_GBS * 1e9)) * 1e3
+        out["b_attention_a2a_outproj_push"] = {"fused_ms": tp_f, "nccl_cublas_ms": tp_u, "speedup": tp_u / tp_f,
+                                               "roofline_ms": roof, "roofline_fraction": roof / tp_f}
         ws.heap.check()
 
     # ---- (c): tensor-parallel AG->GEMM (fc1) and GEMM->RS (fc2) with sequence-sharded activations ----
@@ -133,6 +160,9 @@ def main():
 
     def fused_ag():
         FC.fused_all_gather_linear(tpw, xl, w1)
+
+    def fused_ag_pull():
+        FC.fused_all_gather_linear(tpw, xl, w1, staged=False)
 
     def unfused_ag():
         full = torch.empty(rows * world, H, device="cuda", dtype=torch.bfloat16)
@@ -148,6 +178,7 @@ def main():
         dist.reduce_scatter_tensor(o2, y)
         return o2
     for name, f, u, fl, nb in (("c_tp_ag_gemm", fused_ag, unfused_ag, 2.0 * rows * world * H * F / world, rows * H * 2 * (world - 1)),
+                               ("c_tp_ag_gemm_pull_every_tile", fused_ag_pull, unfused_ag, 2.0 * rows * world * H * F / world, rows * H * 2 * (world - 1)),
                                ("c_tp_gemm_rs", fused_rs, unfused_rs, 2.0 * rows * world * H * F / world, rows * H * 2 * (world - 1))):
         tf, tu = timeit(f, a.iters), timeit(u, a.iters)
         roof = max(fl / (pk * 1e12), nb / (LINK_GBS * 1e9)) * 1e3

@@ -52,6 +52,12 @@ struct GemmParams {
     int n_seg, seg_rows;    // M is n_seg segments of seg_rows rows (n_seg == 1: plain)
     int seg_rot;            // first segment processed (own rank's rows first)
     int my_rank;
+    // mode 2 with staging: remote row segments are copied once into `stage` (this GPU's memory) by dedicated copier
+    // warps while the tensor core works on the local segment; tiles of a remote segment wait for their rows' flag
+    __nv_bfloat16* stage;               // [n_seg * seg_rows, K]
+    const __nv_bfloat16* peer_a[TT_MAX_PEERS];
+    int* stage_flags;                   // [n_seg * tiles_per_seg], set to `stage_epoch` when the rows have landed
+    int stage_epoch;
     // ---- where the output tile goes ----
     int store_mode;         // 0: C (local); 1: column block -> peer_out[col / out_span] (head -> owner);
                             // 2: row segment -> peer_out[segment] staging slot of this rank (reduce-scatter push)
@@ -90,8 +96,17 @@ __device__ __forceinline__ float epi_apply(float acc, float b, float u) {
     return acc * tt::gelu_tanh_grad(u);
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI, bool STAGE = false>
+__global__ void __launch_bounds__(STAGE ? kThreads + 128 : kThreads, 1)
 gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -178,8 +193,26 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                                 am = m0;
                             }
                         } else if (p.a_mode == 2) {
-                            ta = &tmA.m[seg];
-                            am = m0;
+                            if (STAGE && seg != p.my_rank) {
+                                if (kb == 0) {
+                                    // rows of a remote segment: wait (bounded) until the copier warps have landed them
+                                    const int* flag = p.stage_flags + seg * tiles_per_seg + m0 / BM;
+                                    const long long t0 = clock64();
+                                    while (ld_acquire(flag) != p.stage_epoch) {
+                                        if (abort_flag || clock64() - t0 > kWaitCycles) {
+                                            abort_flag = 1;
+                                            goto done;
+                                        }
+                                        __nanosleep(100);
+                                    }
+                                    asm volatile("fence.proxy.async;" ::: "memory");    // generic-proxy writes -> TMA reads
+                                }
+                                ta = &tmA.m[TT_MAX_PEERS];
+                                am = seg * p.seg_rows + m0;
+                            } else {
+                                ta = &tmA.m[seg];
+                                am = m0;
+                            }
                         }
                         tma_load_2d(sa, ta, full_bar(stage), ak, am);
                     } else {
@@ -233,6 +266,25 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                 }
                 umma_commit(tfull_bar(buf));                // accumulator complete
             }
+        }
+    } else if (STAGE && warp >= 6) {
+        // ------------------------------------------------------------ copier warps (all-gather staging)
+        const int tid = threadIdx.x - 192;
+        const int n_items = (p.n_seg - 1) * tiles_per_seg;
+        const long row_vecs = p.K >> 3;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            int seg = 1 + item / tiles_per_seg + p.seg_rot;       // segments in the order the tiles will need them
+            if (seg >= p.n_seg) seg -= p.n_seg;
+            const int mt = item % tiles_per_seg;
+            const int r0 = mt * BM;
+            const int nrows = min(BM, p.seg_rows - r0);
+            const __nv_bfloat16* src = p.peer_a[seg] + (long)r0 * p.K;
+            __nv_bfloat16* dst = p.stage + ((long)seg * p.seg_rows + r0) * p.K;
+            const long nvec = (long)nrows * row_vecs;
+            for (long v = tid; v < nvec; v += 128) tt::st8(dst + v * 8, tt::ld8(src + v * 8));
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");        // only the copier warps take part; no waits in this loop
+            if (tid == 0) st_release(p.stage_flags + seg * tiles_per_seg + mt, p.stage_epoch);
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -377,10 +429,10 @@ done:
     }
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
+template <int BN, bool A_MN, bool B_MN, int EPI, bool STAGE = false>
 int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t st) {
     using C = Cfg<BN>;
-    auto kern = gemm_kernel<BN, A_MN, B_MN, EPI>;
+    auto kern = gemm_kernel<BN, A_MN, B_MN, EPI, STAGE>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -389,7 +441,7 @@ int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, in
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, kThreads, C::kSmemBytes, st>>>(tmA, tmB, p);
+    kern<<<grid, STAGE ? kThreads + 128 : kThreads, C::kSmemBytes, st>>>(tmA, tmB, p);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }
@@ -549,6 +601,9 @@ extern "C" int tt_gemm_bf16(const void* a, const void* b, void* c, const void* b
 //             start at a_row_off in each of them (K == n * a_span).
 //   a_mode 2: all-gather fused into the operand fetch: a_ptrs[r] is rank r's [seg_rows, K] row block; M == n * seg_rows.
 //   b is B[N, K] (b_mn 0) or [K, N] (b_mn 1), always local.
+//             With `stage` ([M, K], this GPU's memory) and `stage_flags` ([n * ceil(seg_rows / 128)] ints, zero at first
+//             use) and a per-launch increasing `stage_epoch`, remote row blocks are copied into `stage` once by
+//             dedicated warps and TMA-loaded from there, instead of crossing NVLink again for every N tile.
 //   store_mode 0: C local.  1: column block j of width out_span goes to out_ptrs[j] (token rows out_row_off + row,
 //             row pitch out_ld): the sequence -> head all-to-all of a data gradient.  2: row segment i goes to
 //             out_ptrs[i] + my_rank * seg_rows * N: partial sums pushed to their owner (reduce-scatter; sum with
@@ -559,7 +614,7 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
                                  const void* a_extra, long lda_extra, const void* b, int b_mn, long ldb, void* c,
                                  long ldc, const void* bias, int M, int N, int K, int seg_rows, int my_rank,
                                  int store_mode, void* const* out_ptrs, int out_span, int out_row_off, long out_ld,
-                                 int* status, void* stream) {
+                                 void* stage, int* stage_flags, int stage_epoch, int* status, void* stream) {
     if (n < 1 || n > TT_MAX_PEERS || M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7) || status == nullptr) return TT_ERR_ARG;
     if (a_mode < 0 || a_mode > 2 || store_mode < 0 || store_mode > 2 || my_rank < 0 || my_rank >= n) return TT_ERR_ARG;
     if (a_mode == 1 && ((a_span % BK) || (long)a_span * n > K)) return TT_ERR_ARG;
@@ -581,6 +636,10 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
         const uint64_t rows = a_mode == 2 ? (uint64_t)seg_rows : (uint64_t)a_rows;
         const uint64_t cols = a_mode == 1 ? (uint64_t)a_span : (uint64_t)K;
         if ((rc = tt_make_tmap_2d(&tmA.m[r], a_ptrs[r], rows, cols, cols, BM, BK)) != TT_OK) return rc;
+    }
+    const bool staged = a_mode == 2 && stage != nullptr && stage_flags != nullptr && n > 1 && store_mode == 0 && !b_mn;
+    if (staged) {
+        if ((rc = tt_make_tmap_2d(&tmA.m[TT_MAX_PEERS], stage, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK)) != TT_OK) return rc;
     }
     if (a_mode == 1 && a_extra != nullptr) {
         const uint64_t cols = (uint64_t)K - (uint64_t)a_span * n;
@@ -615,6 +674,14 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
     p.tiles_m = p.n_seg * ((p.seg_rows + BM - 1) / BM);
     p.tiles_n = (N + BN - 1) / BN;
     cudaStream_t st = (cudaStream_t)stream;
+    if (staged) {
+        p.stage = (__nv_bfloat16*)stage;
+        p.stage_flags = stage_flags;
+        p.stage_epoch = stage_epoch;
+        for (int r = 0; r < n; ++r) p.peer_a[r] = (const __nv_bfloat16*)a_ptrs[r];
+        return BN == 128 ? launch<128, false, false, 0, true>(tmA, tmB, p, sms, st)
+                         : launch<256, false, false, 0, true>(tmA, tmB, p, sms, st);
+    }
     return BN == 128 ? dispatch<128>(false, b_mn != 0, 0, tmA, tmB, p, sms, st)
                      : dispatch<256>(false, b_mn != 0, 0, tmA, tmB, p, sms, st);
 }

@@ -69,7 +69,8 @@ int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* 
 int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off,
                       const void* a_extra, long lda_extra, const void* b, int b_mn, long ldb, void* c, long ldc,
                       const void* bias, int M, int N, int K, int seg_rows, int my_rank, int store_mode,
-                      void* const* out_ptrs, int out_span, int out_row_off, long out_ld, int* status, void* stream);
+                      void* const* out_ptrs, int out_span, int out_row_off, long out_ld, void* stage, int* stage_flags,
+                      int stage_epoch, int* status, void* stream);
 int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias, const void* qw, const void* kw, const float* cos_t,
                       const float* sin_t, void* const* q_ptrs, void* const* k_ptrs, void* const* v_ptrs, int n,
                       int my_rank, void* aux, int M, int heads, int K, int s_in, int s_out, int out_off, int rope_len,

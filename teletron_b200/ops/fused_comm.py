@@ -169,7 +169,7 @@ def _a2a_gemm(ws: UlyssesWorkspace, src_name: str, row_off: int, M: int, w, bias
     call("tt_gemm_comm_bf16", ws.table(src_name), c_int(ws.cp), c_int(1), c_long(ws.S_tot), c_int(ws.h_loc * 128),
          c_int(row_off), ptr(extra), c_long(0 if extra is None else extra.stride(0)), ptr(w), c_int(0), c_long(w.stride(0)),
          ptr(out), c_long(N), ptr(bias), c_int(M), c_int(N), c_int(K), c_int(0), c_int(ws.rank), c_int(0), None, c_int(0),
-         c_int(0), c_long(0), ptr(status_tensor(w.device)), stream())
+         c_int(0), c_long(0), None, None, c_int(0), ptr(status_tensor(w.device)), stream())
     return out
 
 
@@ -223,7 +223,7 @@ class _FusedAllToAllLinear(torch.autograd.Function):
         call("tt_gemm_comm_bf16", _table([dy2.data_ptr()]), c_int(ws.cp), c_int(0), c_long(ws.s), c_int(0), c_int(0), None,
              c_long(0), ptr(w), c_int(1), c_long(w.stride(0)), ptr(dex), c_long(0 if dex is None else dex.stride(0)), None,
              c_int(ws.s), c_int(K), c_int(w.shape[0]), c_int(0), c_int(ws.rank), c_int(1), ws.table("do"), c_int(span),
-             c_int(ws.video_off + ws.rank * ws.s), c_long(span), ptr(status_tensor(dev)), stream())
+             c_int(ws.video_off + ws.rank * ws.s), c_long(span), None, None, c_int(0), ptr(status_tensor(dev)), stream())
         # text rows: every rank holds the full gradient; keep this rank's heads, scaled by cp (the gather's "up" rule)
         dot_full = gemm.gemm_nn(dyt2, wt)
         do_local = ws.token_major("do")
@@ -252,7 +252,8 @@ def _local_gemm_extra(ws: UlyssesWorkspace, a_rows: torch.Tensor, extra, w, bias
     out = torch.empty(M, N, dtype=BF16, device=w.device)
     call("tt_gemm_comm_bf16", _table([a_rows.data_ptr()]), c_int(1), c_int(1), c_long(M), c_int(G), c_int(0), ptr(extra),
          c_long(extra.stride(0)), ptr(w), c_int(0), c_long(w.stride(0)), ptr(out), c_long(N), ptr(bias), c_int(M), c_int(N),
-         c_int(K), c_int(0), c_int(0), c_int(0), None, c_int(0), c_int(0), c_long(0), ptr(status_tensor(w.device)), stream())
+         c_int(K), c_int(0), c_int(0), c_int(0), None, c_int(0), c_int(0), c_long(0), None, None, c_int(0),
+         ptr(status_tensor(w.device)), stream())
     return out
 
 
@@ -332,7 +333,7 @@ class _FusedAttentionOutProj(torch.autograd.Function):
         call("tt_gemm_comm_bf16", _table([dy2.data_ptr()]), c_int(ws.cp), c_int(0), c_long(s), c_int(0), c_int(0), None,
              c_long(0), ptr(w), c_int(1), c_long(w.stride(0)), ptr(dex), c_long(0 if dex is None else dex.stride(0)), None,
              c_int(s), c_int(K), c_int(w.shape[0]), c_int(0), c_int(ws.rank), c_int(1), ws.table("do"), c_int(span),
-             c_int(ws.video_off + ws.rank * s), c_long(span), ptr(status_tensor(dev)), stream())
+             c_int(ws.video_off + ws.rank * s), c_long(span), None, None, c_int(0), ptr(status_tensor(dev)), stream())
         # text rows are replicated: keep this rank's heads, scaled by cp
         dot_full = gemm.gemm_nn(dyt2, wt)
         do_local = ws.token_major("do")
@@ -368,9 +369,13 @@ class TPWorkspace:
         self.off_a = self.heap.alloc(a_bytes)
         self.off_s = self.heap.alloc(s_bytes)
         self.k_max, self.n_max = k_max, n_max
+        dev = self.heap.device
+        self.stage = torch.empty(self.tp * rows_local * k_max, dtype=BF16, device=dev)
+        self.flags = torch.zeros(self.tp * ((rows_local + 127) // 128), dtype=torch.int32, device=dev)
+        self.epoch = 0
 
 
-def fused_all_gather_linear(ws: TPWorkspace, x_local: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+def fused_all_gather_linear(ws: TPWorkspace, x_local: torch.Tensor, w: torch.Tensor, bias=None, staged: bool = True) -> torch.Tensor:
     """``all_gather(x_local over rows) @ w^T + bias``: every rank's row block is TMA-loaded from its owner while the
     tensor core works; this rank's own rows are scheduled first.  ``x_local [rows, K]``, ``w [N, K]`` (column-parallel shard)."""
     rows, K = x_local.shape
@@ -383,9 +388,13 @@ def fused_all_gather_linear(ws: TPWorkspace, x_local: torch.Tensor, w: torch.Ten
     N = w.shape[0]
     M = rows * ws.tp
     out = torch.empty(M, N, dtype=BF16, device=w.device)
+    # remote row blocks are copied once into this local staging buffer by the kernel's copier warps
+    stage = ws.stage[: M * K].view(M, K) if staged else None
+    ws.epoch += 1
     call("tt_gemm_comm_bf16", ws.heap.ptr_table(ws.off_a), c_int(ws.tp), c_int(2), c_long(rows), c_int(0), c_int(0), None,
          c_long(0), ptr(w), c_int(0), c_long(w.stride(0)), ptr(out), c_long(N), ptr(bias), c_int(M), c_int(N), c_int(K),
-         c_int(rows), c_int(ws.rank), c_int(0), None, c_int(0), c_int(0), c_long(0), ptr(status_tensor(w.device)), stream())
+         c_int(rows), c_int(ws.rank), c_int(0), None, c_int(0), c_int(0), c_long(0), ptr(stage), ptr(ws.flags), c_int(ws.epoch),
+         ptr(status_tensor(w.device)), stream())
     return out
 
 
@@ -400,8 +409,8 @@ def fused_linear_reduce_scatter(ws: TPWorkspace, x: torch.Tensor, w: torch.Tenso
     ws.heap.barrier()              # previous partials have been consumed everywhere
     call("tt_gemm_comm_bf16", _table([x.data_ptr()]), c_int(ws.tp), c_int(0), c_long(M), c_int(0), c_int(0), None, c_long(0),
          ptr(w), c_int(0), c_long(w.stride(0)), None, c_long(0), None, c_int(M), c_int(N), c_int(K), c_int(ws.rows),
-         c_int(ws.rank), c_int(2), ws.heap.ptr_table(ws.off_s), c_int(0), c_int(0), c_long(N), ptr(status_tensor(x.device)),
-         stream())
+         c_int(ws.rank), c_int(2), ws.heap.ptr_table(ws.off_s), c_int(0), c_int(0), c_long(N), None, None, c_int(0),
+         ptr(status_tensor(x.device)), stream())
     ws.heap.barrier()              # all partials have landed
     out = torch.empty(ws.rows, N, dtype=BF16, device=x.device)
     stage = ws.heap.tensor(ws.off_s, (ws.tp, ws.rows, N), BF16)
