@@ -8,6 +8,7 @@
 // a normalised copy of the activations, and every launch on the caller's stream.
 #include "common.cuh"
 #include "teletron_b200.h"
+#include "teletron_b200_noalloc.h"
 
 namespace {
 
@@ -472,6 +473,56 @@ extern "C" int tt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
     cudaStream_t st = (cudaStream_t)stream;
     const int nblk = pick_blocks(rows, 1);
     const int threads = (((cols >> 3) + 31) / 32) * 32;
+    rmsnorm_bwd_kernel<<<nblk, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                 (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols);
+    TT_CHECK_LAUNCH();
+    column_finalize_kernel<<<dim3((cols + 255) / 256, 1, 1), 256, 0, st>>>(partials, (__nv_bfloat16*)dw, nullptr, nullptr,
+                                                                         1, nblk, cols);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot allocate device memory (declared in teletron_b200_noalloc.h)
+// ---------------------------------------------------------------------------------------------
+// The partial column sums that tt_rmsnorm_bwd takes from its caller live here instead, in a fixed array that
+// is part of the library image: every GPU that loads the library carries these 2 MiB until the process exits.
+static __device__ __align__(256) float g_rmsnorm_noalloc_partials[TT_NOALLOC_MAX_BLOCKS * TT_NOALLOC_MAX_COLS];
+
+namespace {
+// Device address of the array above, per device.  In host code the array's name is only a handle for the
+// runtime's symbol table, never something a kernel can dereference, so the address is looked up once per device.
+float* g_noalloc_ptr[64] = {nullptr};
+
+int noalloc_scratch(float** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return tt_record_cuda(e);
+    if (dev < 0 || dev >= 64) return TT_ERR_LIMIT;
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_rmsnorm_noalloc_partials);     // resolves against the current device
+        if (e != cudaSuccess) return tt_record_cuda(e);
+        g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return TT_OK;
+}
+}  // namespace
+
+extern "C" int tt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
+                                      long rows, int cols, void* stream) {
+    if (bad_cols(cols) || rows <= 0) return TT_ERR_ARG;
+    if (cols > TT_NOALLOC_MAX_COLS) return TT_ERR_LIMIT;
+    float* partials = nullptr;
+    const int rc = noalloc_scratch(&partials);
+    if (rc != TT_OK) return rc;
+    int nblk = pick_blocks(rows, 1);
+    if (nblk > TT_NOALLOC_MAX_BLOCKS) nblk = TT_NOALLOC_MAX_BLOCKS;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = (((cols >> 3) + 31) / 32) * 32;
+    // every one of the nblk partial rows is fully rewritten by its block before the finalize pass reads it,
+    // so nothing left behind by an earlier call can leak into this one
     rmsnorm_bwd_kernel<<<nblk, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                  (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols);
     TT_CHECK_LAUNCH();
