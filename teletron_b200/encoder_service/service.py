@@ -19,6 +19,7 @@ flat message per sample to the first rank of each TP x CP block over ``torch.dis
 from __future__ import annotations
 
 import collections
+import threading
 import time
 from typing import Callable, Dict, List, Optional
 
@@ -37,17 +38,48 @@ class EncoderTimeout(RuntimeError):
     pass
 
 
-def _wait(req, timeout: Optional[float], what: str):
-    """Bounded wait on a p2p request: polls ``is_completed`` so a lost peer surfaces as an exception."""
-    if timeout is None or timeout <= 0:
-        req.wait()
-        return
-    t0 = time.monotonic()
-    while not req.is_completed():
-        if time.monotonic() - t0 > timeout:
-            raise EncoderTimeout(f"timed out after {timeout:.1f}s waiting for {what}")
-        time.sleep(0.001)
-    req.wait()
+class _Request:
+    """A p2p request whose completion can be polled on every backend.
+
+    NCCL requests answer ``is_completed()`` from a CUDA event.  Gloo requests only make progress inside ``wait()``,
+    and a ``wait(timeout)`` that runs out tears the connection down, so there a helper thread sits in ``wait()`` and
+    sets an event (the CPU path is for tests and small jobs; one short-lived thread per message is acceptable)."""
+
+    def __init__(self, req):
+        self._req = req
+        self._event = None
+        self._error = None
+        if dist.get_backend() != "nccl":
+            self._event = threading.Event()
+            threading.Thread(target=self._run, daemon=True).start()
+
+    def _run(self):
+        try:
+            self._req.wait()
+        except Exception as e:          # a closed connection: reported to whoever waits
+            self._error = e
+        self._event.set()
+
+    def done(self) -> bool:
+        if self._event is not None:
+            return self._event.is_set()
+        return self._req.is_completed()
+
+    def wait(self, timeout: Optional[float], what: str) -> None:
+        """Bounded wait: a lost peer surfaces as :class:`EncoderTimeout` instead of a hang."""
+        if self._event is not None:
+            if not self._event.wait(timeout if timeout and timeout > 0 else None):
+                raise EncoderTimeout(f"timed out after {timeout:.1f}s waiting for {what}")
+            if self._error is not None:
+                raise EncoderTimeout(f"{what}: {self._error}")
+            return
+        if timeout and timeout > 0:
+            t0 = time.monotonic()
+            while not self._req.is_completed():
+                if time.monotonic() - t0 > timeout:
+                    raise EncoderTimeout(f"timed out after {timeout:.1f}s waiting for {what}")
+                time.sleep(0.001)
+        self._req.wait()
 
 
 class Encoders:
@@ -61,13 +93,22 @@ class Encoders:
         self.vae, self.text, self.clip = vae, text, clip
 
     @staticmethod
-    def build_default(device, dtype=torch.bfloat16, vae_tiling: bool = True, max_text_len: int = 256) -> "Encoders":
+    def build_default(device, dtype=torch.bfloat16, vae_tiling: bool = True, max_text_len: int = 256,
+                      preset: str = "default", text_dim: int = 4096, pooled_dim: int = 768) -> "Encoders":
+        """The real encoders (random weights unless paths are configured): a 32-layer LLaMA-style decoder, CLIP-L text
+        and the 3-D causal VAE; ``preset="tiny"`` shrinks all three for CPU tests."""
         from ..models.vae import AutoencoderKLHunyuanVideo
-        from ..models.text_encoders import ClipTextEncoder, LlamaTextEncoder
-        vae = AutoencoderKLHunyuanVideo().to(device, dtype).eval()
+        from ..models.text_encoders import ClipTextEncoder, LlamaTextEncoder, clip_text_config, llama_config
+        if preset == "tiny":
+            vae = AutoencoderKLHunyuanVideo(block_out_channels=(32, 32, 32, 32)).to(device, dtype).eval()
+            llama = LlamaTextEncoder(max_length=max_text_len, device=device, dtype=dtype,
+                                     config=llama_config(2, text_dim, 4, 2, 2 * text_dim, 1000))
+            clip = ClipTextEncoder(device=device, dtype=dtype, max_length=16, config=clip_text_config(2, pooled_dim, 4, 500, 16))
+        else:
+            vae = AutoencoderKLHunyuanVideo().to(device, dtype).eval()
+            llama = LlamaTextEncoder(max_length=max_text_len, device=device, dtype=dtype)
+            clip = ClipTextEncoder(device=device, dtype=dtype)
         vae.enable_tiling(vae_tiling)
-        llama = LlamaTextEncoder(max_length=max_text_len, device=device, dtype=dtype)
-        clip = ClipTextEncoder(device=device, dtype=dtype)
         sf = 0.476986
 
         @torch.no_grad()
@@ -99,23 +140,38 @@ def encode_sample(sample: Dict, enc: Encoders, spec: MessageSpec, seq: int, devi
                         first_lat[0].to(device, torch.bfloat16), latents[0].to(device, torch.bfloat16))
 
 
+def spec_from_args(args) -> MessageSpec:
+    return MessageSpec.from_flags(args.num_frames, args.video_resolution, args.encoder_max_text_len,
+                                  args.encoder_text_dim, args.encoder_pooled_dim)
+
+
 def producer_loop(pairs: List[CommPair], iterators: Dict[int, object], encode: Callable[[Dict, int], torch.Tensor],
                   start_seq: Dict[int, int], max_items: Optional[int] = None, idle_sleep: float = 0.002,
-                  drop: Optional[Callable[[int, int], bool]] = None) -> Dict[int, int]:
+                  drop: Optional[Callable[[int, int], bool]] = None, stall_timeout: Optional[float] = None) -> Dict[int, int]:
     """Round-robin service of all consumers: keep up to ``QUEUE_DEPTH`` encoded samples per consumer and
     one outstanding ``isend`` each.  ``drop(consumer, seq)`` is a host-side fault-injection hook for the
-    tests (a message that is encoded but never sent).  Returns the number of messages sent per consumer."""
+    tests (a message that is encoded but never sent).  A consumer whose receive does not match a send within
+    ``stall_timeout`` seconds is taken for lost and no longer served, so one dead DiT block cannot starve the
+    others.  Returns the number of messages sent per consumer."""
     queues = {p.consumer: collections.deque() for p in pairs}
     inflight = {p.consumer: collections.deque() for p in pairs}
     seq = dict(start_seq)
     sent = {p.consumer: 0 for p in pairs}
     produced = {p.consumer: 0 for p in pairs}
     exhausted = set()
+    lost = set()
     while True:
         progress = False
         for p in pairs:
             c = p.consumer
-            while inflight[c] and inflight[c][0][0].is_completed():
+            if c in lost:
+                continue
+            if stall_timeout and inflight[c] and time.monotonic() - inflight[c][0][2] > stall_timeout:
+                lost.add(c)
+                queues[c].clear()
+                inflight[c].clear()
+                continue
+            while inflight[c] and inflight[c][0][0].done():
                 inflight[c].popleft()
                 progress = True
             if c not in exhausted and len(queues[c]) < QUEUE_DEPTH and (max_items is None or produced[c] < max_items):
@@ -132,11 +188,11 @@ def producer_loop(pairs: List[CommPair], iterators: Dict[int, object], encode: C
                 s, msg = queues[c].popleft()
                 if drop is not None and drop(c, s):
                     continue
-                inflight[c].append((dist.isend(msg, dst=c), msg))
+                inflight[c].append((_Request(dist.isend(msg, dst=c)), msg, time.monotonic()))
                 sent[c] += 1
                 progress = True
-        done = all((c in exhausted or (max_items is not None and produced[c] >= max_items))
-                   and not queues[c] and not inflight[c] for c in queues)
+        done = all(c in lost or ((c in exhausted or (max_items is not None and produced[c] >= max_items))
+                                 and not queues[c] and not inflight[c]) for c in queues)
         if done:
             return sent
         if not progress:
@@ -150,16 +206,18 @@ def producer_process(args, train_valid_test_datasets_provider: Callable, encoder
     pairs = ps.get_producer_pairs()
     if not pairs:
         return
-    spec = MessageSpec.from_flags(args.num_frames, args.video_resolution)
-    enc = encoders or Encoders.build_default(device, args.params_dtype, vae_tiling=bool(args.vae_tiling))
+    spec = spec_from_args(args)
+    enc = encoders or Encoders.build_default(device, args.params_dtype, vae_tiling=bool(args.vae_tiling),
+                                             max_text_len=args.encoder_max_text_len, preset=args.encoder_preset,
+                                             text_dim=args.encoder_text_dim, pooled_dim=args.encoder_pooled_dim)
     # handshake: every consumer tells us the iteration it resumes from (training.py:208-220, producer.py:137-153)
     start = {}
     reqs = []
     for p in pairs:
         t = torch.zeros(1, dtype=torch.int64, device=device)
-        reqs.append((p, t, dist.irecv(t, src=p.consumer)))
+        reqs.append((p, t, _Request(dist.irecv(t, src=p.consumer))))
     for p, t, r in reqs:
-        _wait(r, args.distributed_timeout_minutes * 60.0, f"handshake from consumer {p.consumer}")
+        r.wait(args.distributed_timeout_minutes * 60.0, f"handshake from consumer {p.consumer}")
         start[p.consumer] = int(t.item())
     iterators = {}
     for p in pairs:
@@ -178,7 +236,7 @@ class EncoderConsumer:
                  timeout: Optional[float] = None, fallback: Optional[Callable[[], Dict]] = None):
         self.pair = pair
         self.device = device
-        self.spec = spec or MessageSpec.from_flags(args.num_frames, args.video_resolution)
+        self.spec = spec or spec_from_args(args)
         self.timeout = timeout if timeout is not None else (args.distributed_timeout_minutes * 60.0 if args else None)
         self.fallback = fallback
         self._bufs = [torch.empty(self.spec.numel, dtype=torch.bfloat16, device=device) for _ in range(2)]
@@ -189,11 +247,14 @@ class EncoderConsumer:
         self._args = args
         self.bytes_received = 0
 
-    def handshake(self, iteration: int) -> None:
+    def handshake(self, iteration: int, num_messages: Optional[int] = None) -> None:
+        """Tell the producer where to resume; ``num_messages`` bounds how many receives will ever be posted."""
         t = torch.tensor([iteration], dtype=torch.int64, device=self.device)
         dist.isend(t, dst=self.pair.producer).wait()
         self._seq = iteration
-        if self._args is not None:
+        if num_messages is not None:
+            self._to_post = num_messages
+        elif self._args is not None:
             # never leave an unmatched receive behind at shutdown
             self._to_post = max(0, self._args.train_iters - iteration) * self._args.num_microbatches
         self._post()
@@ -204,7 +265,7 @@ class EncoderConsumer:
                 self._req = None
                 return
             self._to_post -= 1
-        self._req = dist.irecv(self._bufs[self._slot], src=self.pair.producer)
+        self._req = _Request(dist.irecv(self._bufs[self._slot], src=self.pair.producer))
 
     def next_batch(self) -> Dict[str, torch.Tensor]:
         """The sample for this step; immediately re-posts the receive for the next one."""
@@ -213,7 +274,7 @@ class EncoderConsumer:
         if self._req is None:
             raise RuntimeError("the encoder stream is exhausted (all scheduled samples were received)")
         try:
-            _wait(self._req, self.timeout, f"sample {self._seq} from encoder rank {self.pair.producer}")
+            self._req.wait(self.timeout, f"sample {self._seq} from encoder rank {self.pair.producer}")
             msg = self._bufs[self._slot]
             out = unpack_message(self.spec, msg, expect_seq=self._seq)
         except (EncoderTimeout, ProtocolError):

@@ -85,6 +85,11 @@ def _add_parallel_args(p):
     g.add_argument("--distributed-timeout-minutes", type=float, default=10)
     g.add_argument("--distributed-vae", action="store_true")
     g.add_argument("--distributed-vae-world-size", type=int, default=0)
+    g.add_argument("--encoder-preset", type=str, default="default", choices=["default", "tiny"],
+                   help="size of the VAE / text encoders on the encoder ranks (tiny: CPU tests)")
+    g.add_argument("--encoder-text-dim", type=int, default=None)
+    g.add_argument("--encoder-pooled-dim", type=int, default=None)
+    g.add_argument("--encoder-max-text-len", type=int, default=256)
     g.add_argument("--nccl-communicator-config-path", type=str, default=None)
     g.add_argument("--tp-comm-overlap", action="store_true")
     g.add_argument("--local-rank", "--local_rank", type=int, default=None)
@@ -189,6 +194,11 @@ def validate_args(args, world_size: Optional[int] = None):
         args.lr_decay_iters = args.train_iters
     if args.lr_warmup_fraction:
         args.lr_warmup_iters = int(args.lr_warmup_fraction * args.lr_decay_iters)
+    tiny = args.model_size == "tiny"
+    if args.encoder_text_dim is None:
+        args.encoder_text_dim = 64 if tiny else 4096
+    if args.encoder_pooled_dim is None:
+        args.encoder_pooled_dim = 32 if tiny else 768
     args.iteration = 0
     args.consumed_train_samples = 0
     return args

@@ -29,7 +29,13 @@ def print_rank_0(*a, **kw) -> None:
 
 
 def print_rank_last(*a, **kw) -> None:
-    if (not dist.is_initialized()) or dist.get_rank() == dist.get_world_size() - 1:
+    """Printed by the last DiT rank (encoder ranks sit behind it and report nothing)."""
+    last = True
+    if dist.is_initialized():
+        from ..parallel import state as ps
+        n = ps.state().dit_world_size if ps.model_parallel_is_initialized() else dist.get_world_size()
+        last = dist.get_rank() == n - 1
+    if last:
         print(*a, **kw, flush=True)
 
 
@@ -109,9 +115,12 @@ class Timers:
             v = self._timers[n].elapsed(reset)
             mx = mn = v
             if dist.is_initialized() and dist.get_world_size() > 1:
+                from ..parallel import state as ps
+                # encoder ranks never reach a timer report: reduce over the DiT ranks only
+                group = ps.get_transformer_model_group() if ps.model_parallel_is_initialized() else None
                 dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
                 t = torch.tensor([v, -v], dtype=torch.float64, device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
                 mx, mn = float(t[0]), -float(t[1])
             out[n] = {"max_ms": mx, "min_ms": mn}
         return out
