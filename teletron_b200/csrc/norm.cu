@@ -183,8 +183,19 @@ __global__ void column_finalize_kernel(const float* __restrict__ partials, __nv_
     const int k = blockIdx.y;
     const long b = blockIdx.z;
     if (c >= cols) return;
-    float s = 0.f;
-    for (int i = 0; i < nblk; ++i) s += partials[((b * nblk + i) * K + k) * (long)cols + c];
+    // four independent chains keep several loads in flight; the order is fixed, so the sum is deterministic
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    const float* p = partials + (b * nblk * K + k) * (long)cols + c;
+    const long step = (long)K * cols;
+    int i = 0;
+    for (; i + 3 < nblk; i += 4) {
+        s0 += p[(i + 0) * step];
+        s1 += p[(i + 1) * step];
+        s2 += p[(i + 2) * step];
+        s3 += p[(i + 3) * step];
+    }
+    for (; i < nblk; ++i) s0 += p[i * step];
+    const float s = (s0 + s1) + (s2 + s3);
     __nv_bfloat16* o = k == 0 ? out0 : (k == 1 ? out1 : out2);
     if (o != nullptr) o[b * cols + c] = __float2bfloat16(s);
 }

@@ -180,15 +180,29 @@ __global__ void __launch_bounds__(256) qkv_post_bwd_kernel(
     }
 }
 
-__global__ void qkv_weight_finalize_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ dqw,
-                                           __nv_bfloat16* __restrict__ dkw, int nparts) {
-    // 256 threads: thread t sums column t of the [nparts][256] partial matrix
-    const int t = threadIdx.x;
-    float s = 0.f;
-    for (int i = blockIdx.x; i < nparts; i += gridDim.x) s += partials[(long)i * 256 + t];
-    // single block keeps it deterministic
-    if (t < D) dqw[t] = __float2bfloat16(s);
-    else dkw[t - D] = __float2bfloat16(s);
+__global__ void __launch_bounds__(1024) qkv_weight_finalize_kernel(const float* __restrict__ partials,
+                                                                   __nv_bfloat16* __restrict__ dqw,
+                                                                   __nv_bfloat16* __restrict__ dkw, int nparts) {
+    // One block (fixed summation order => deterministic).  1024 threads = 4 row groups x 256 columns; every thread
+    // keeps 8 independent loads in flight, then the 4 groups are folded through shared memory in a fixed order.
+    __shared__ float fold[4][256];
+    const int c = threadIdx.x & 255, g = threadIdx.x >> 8;
+    float acc[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+    int i = g;
+    for (; i + 28 < nparts; i += 32) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] += partials[(long)(i + 4 * u) * 256 + c];
+    }
+    for (; i < nparts; i += 4) acc[0] += partials[(long)i * 256 + c];
+    fold[g][c] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+    __syncthreads();
+    if (g == 0) {
+        const float s = (fold[0][c] + fold[1][c]) + (fold[2][c] + fold[3][c]);
+        if (c < D) dqw[c] = __float2bfloat16(s);
+        else dkw[c - D] = __float2bfloat16(s);
+    }
 }
 
 inline int pick_grid(long nwork) {
@@ -236,7 +250,7 @@ extern "C" int tt_qkv_post_bwd_peer(void* const* dq_ptrs, void* const* dk_ptrs, 
                                               (const __nv_bfloat16*)kw, cos_t, sin_t, (__nv_bfloat16*)dqkv, partials,
                                               rows, heads, seq_in, seq_out, out_offset, rope_len, eps);
     TT_CHECK_LAUNCH();
-    qkv_weight_finalize_kernel<<<1, 256, 0, st>>>(partials, (__nv_bfloat16*)dqw, (__nv_bfloat16*)dkw, grid * 8);
+    qkv_weight_finalize_kernel<<<1, 1024, 0, st>>>(partials, (__nv_bfloat16*)dqw, (__nv_bfloat16*)dkw, grid * 8);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }
