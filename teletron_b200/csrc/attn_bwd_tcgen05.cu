@@ -11,7 +11,7 @@
 // Both run the same pipeline.  Stationary operands [128 x 128] are loaded once; streamed chunks
 // [64 x 128] x 2 go through a 4-stage TMA ring.  T1 / T2 (128 x 64 fp32 each) are double buffered in
 // tensor memory, so the tensor core computes the next chunk's T products and the previous chunk's
-// accumulator updates while the four softmax warps (one stationary row per thread) turn the current
+// accumulator updates while the eight softmax warps (one stationary row x 32 streamed columns per thread) turn the current
 // T1 / T2 into bf16 P / dS, written back over T1 / T2 in tensor memory and consumed from there as the
 // A operand of the accumulator MMAs.  The streamed chunk is used twice from the same shared-memory bytes:
 // as a K-major B operand for the T products and as an MN-major B operand for the accumulator updates.
@@ -34,7 +34,7 @@ constexpr int D = 128;
 constexpr int BS = 128;            // stationary rows
 constexpr int BC = 64;             // streamed rows per chunk
 constexpr int kStages = 4;
-constexpr int kThreads = 192;      // warp 0 TMA, warp 1 MMA, warps 2-5 softmax / epilogue
+constexpr int kThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2-9 softmax / epilogue (two warpgroups)
 constexpr int kStatSlab = BS * 128;        // [128 x 64] slab: 16 KB
 constexpr int kStatTile = 2 * kStatSlab;   // [128 x 128]: 32 KB
 constexpr int kChunkSlab = BC * 128;       // [64 x 64] slab: 8 KB
@@ -111,7 +111,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         for (int u = 0; u < 2; ++u) {
             mbar_init(t_full(u), 1);
-            mbar_init(p_full(u), 4);
+            mbar_init(p_full(u), 8);
         }
         mbar_init(acc_final, 1);
         fence_barrier_init();
@@ -219,7 +219,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             umma_commit(acc_final);
         }
     } else {
-        // ------------------------------------------------------------ softmax / dS (one stationary row per thread)
+        // ------------------------------------------------------------ softmax / dS
+        // Two warpgroups share every chunk: a thread owns one stationary row and 32 of the chunk's 64 streamed
+        // columns (warpgroup 0: columns [0, 32), warpgroup 1: [32, 64)), so two warps per scheduler hide each
+        // other's tcgen05.ld / exp2 latency.
+        const int half = (warp - 2) >> 2;
         const int quad = warp & 3;
         const int srow = quad * 32 + lane;                 // row within the stationary tile
         const int row = r0 + srow;                         // key (KVS) or query index
@@ -244,9 +248,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!mbar_wait(t_full(u), (uint32_t)(c >> 1) & 1u, &abort_flag)) goto done;
             tc_fence_after();
             const uint32_t t1 = tmem + lane_sel + u * 128, t2 = t1 + 64;
-            uint32_t pk[32], dk[32];
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            uint32_t pk[16], dk[16];
+            {
                 uint32_t a[32], g[32];
                 tmem_ld_32x32(t1 + half * 32, a);
                 tmem_ld_32x32(t2 + half * 32, g);
@@ -284,16 +287,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     const float2 ds = __fmul2_rn(pr, dp);
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(pr.x, pr.y);
                     const __nv_bfloat162 db = __floats2bfloat162_rn(ds.x, ds.y);
-                    pk[half * 16 + i] = *reinterpret_cast<const uint32_t*>(&pb);
-                    dk[half * 16 + i] = *reinterpret_cast<const uint32_t*>(&db);
+                    pk[i] = *reinterpret_cast<const uint32_t*>(&pb);
+                    dk[i] = *reinterpret_cast<const uint32_t*>(&db);
                 }
             }
-            if (KVS) {
-                tmem_st_32x16(t1, pk);
-                tmem_st_32x16(t1 + 16, pk + 16);
-            }
-            tmem_st_32x16(t2, dk);
-            tmem_st_32x16(t2 + 16, dk + 16);
+            if (KVS) tmem_st_32x16(t1 + half * 16, pk);
+            tmem_st_32x16(t2 + half * 16, dk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -311,7 +310,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float mul = (KVS && which == 0) ? 1.f : p.scale;
             const uint32_t tacc = tmem + lane_sel + 256 + which * 128;
 #pragma unroll 1
-            for (int cch = 0; cch < D / 32; ++cch) {
+            for (int cch = half * 2; cch < half * 2 + 2; ++cch) {      // each warpgroup stores half of the columns
                 uint32_t r[32];
                 tmem_ld_32x32(tacc + cch * 32, r);
                 tmem_ld_wait();

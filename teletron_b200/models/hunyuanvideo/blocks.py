@@ -43,12 +43,34 @@ def _mark(param: nn.Parameter, *, partition_dim: Optional[int], full_shape: Sequ
     param.tensor_model_parallel = partition_dim is not None
 
 
+def tp_region_input(x: torch.Tensor, sequence_parallel: bool) -> torch.Tensor:
+    """What a column-parallel linear consumes: the replicated activation (gradients all-reduced), or with sequence
+    parallelism the all-gather of the token blocks (gradients reduce-scattered)."""
+    g = ps.get_tensor_model_parallel_group()
+    if sequence_parallel:
+        return M.gather_from_sequence_parallel_region(x, g, dim=1)
+    return M.copy_to_tensor_model_parallel_region(x, g)
+
+
+def tp_region_output(y: torch.Tensor, sequence_parallel: bool, row_splits: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Sum of the row-parallel partial products: all-reduce, or with sequence parallelism a reduce-scatter over the
+    token dim.  ``row_splits`` names token groups (video, text) that are sharded separately."""
+    g = ps.get_tensor_model_parallel_group()
+    if not sequence_parallel:
+        return M.reduce_from_tensor_model_parallel_region(y, g)
+    if row_splits is None:
+        return M.reduce_scatter_to_sequence_parallel_region(y, g, dim=1)
+    parts = [M.reduce_scatter_to_sequence_parallel_region(t, g, dim=1) for t in y.split(list(row_splits), dim=1)]
+    return torch.cat(parts, dim=1)
+
+
 class ColumnParallelLinear(nn.Module):
     """``y = act(x W^T + b)`` with ``W`` sharded over output features (rows)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, tp: int = 1,
-                 device=None, dtype=None):
+                 sequence_parallel: bool = False, device=None, dtype=None):
         super().__init__()
+        self.sequence_parallel = sequence_parallel and tp > 1
         if out_features % tp:
             raise ValueError(f"out_features {out_features} not divisible by tp {tp}")
         self.in_features, self.out_features, self.tp = in_features, out_features, tp
@@ -60,8 +82,10 @@ class ColumnParallelLinear(nn.Module):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, x: torch.Tensor, activation: Optional[str] = None) -> torch.Tensor:
-        x = M.copy_to_tensor_model_parallel_region(x, ps.get_tensor_model_parallel_group())
+    def forward(self, x: torch.Tensor, activation: Optional[str] = None, in_region: bool = False) -> torch.Tensor:
+        """``in_region``: the caller already applied :func:`tp_region_input` (one gather shared by several linears)."""
+        if not in_region:
+            x = tp_region_input(x, self.sequence_parallel)
         return ops.linear(x, self.weight, self.bias, activation)
 
 
@@ -74,8 +98,10 @@ class RowParallelLinear(nn.Module):
     """
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, tp: int = 1,
-                 input_partitions: Optional[Sequence[int]] = None, device=None, dtype=None):
+                 input_partitions: Optional[Sequence[int]] = None, sequence_parallel: bool = False,
+                 device=None, dtype=None):
         super().__init__()
+        self.sequence_parallel = sequence_parallel and tp > 1
         if in_features % tp:
             raise ValueError(f"in_features {in_features} not divisible by tp {tp}")
         self.in_features, self.out_features, self.tp = in_features, out_features, tp
@@ -85,15 +111,17 @@ class RowParallelLinear(nn.Module):
         if bias:
             self.bias = nn.Parameter(torch.empty(out_features, device=device, dtype=dtype))
             _mark(self.bias, partition_dim=None, full_shape=(out_features,), init="zeros")
+            # with sequence parallelism every rank adds the bias to its token block only: the gradient is a partial sum
+            self.bias.tp_partial_grad = self.sequence_parallel
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """Projection, TP all-reduce, bias (bias is added once, after the reduction)."""
+    def forward(self, x: torch.Tensor, row_splits: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Projection, TP all-reduce (or reduce-scatter over tokens), bias (added once, after the reduction)."""
         if self.tp == 1:
             return ops.linear(x, self.weight, self.bias)
         y = ops.linear(x, self.weight, None)
-        y = M.reduce_from_tensor_model_parallel_region(y, ps.get_tensor_model_parallel_group())
+        y = tp_region_output(y, self.sequence_parallel, row_splits)
         return y if self.bias is None else y + self.bias
 
 
@@ -123,25 +151,34 @@ class AdaLNModulation(nn.Module):
     through :func:`teletron_b200.ops.layernorm_modulate`.
     """
 
-    def __init__(self, dim: int, n_chunks: int, tp: int = 1, device=None, dtype=None):
+    def __init__(self, dim: int, n_chunks: int, tp: int = 1, sequence_parallel: bool = False, device=None, dtype=None):
         super().__init__()
         self.n_chunks = n_chunks
+        self.sequence_parallel = sequence_parallel and tp > 1
+        # temb is replicated (never token-sharded): the linear itself takes no sequence-parallel gather
         self.linear = ColumnParallelLinear(dim, n_chunks * dim, bias=True, tp=tp, device=device, dtype=dtype)
 
     def forward(self, temb: torch.Tensor) -> Tuple[torch.Tensor, ...]:
         emb = self.linear(F.silu(temb))
-        emb = M.gather_from_tensor_model_parallel_region(emb, ps.get_tensor_model_parallel_group())
+        g = ps.get_tensor_model_parallel_group()
+        if self.sequence_parallel:
+            # each rank modulates its own token block, so the vectors' gradients are partial sums over TP
+            emb = M.gather_from_tensor_model_parallel_region_reduce_grad(emb, g)
+        else:
+            emb = M.gather_from_tensor_model_parallel_region(emb, g)
         return emb.chunk(self.n_chunks, dim=1)
 
 
 class ParallelMLP(nn.Module):
     """``linear_fc1`` (column-parallel) -> activation -> ``linear_fc2`` (row-parallel)."""
 
-    def __init__(self, dim: int, hidden: int, activation: str, tp: int = 1, device=None, dtype=None):
+    def __init__(self, dim: int, hidden: int, activation: str, tp: int = 1, sequence_parallel: bool = False,
+                 device=None, dtype=None):
         super().__init__()
         self.activation = activation
-        self.linear_fc1 = ColumnParallelLinear(dim, hidden, tp=tp, device=device, dtype=dtype)
-        self.linear_fc2 = RowParallelLinear(hidden, dim, tp=tp, device=device, dtype=dtype)
+        kw = dict(tp=tp, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+        self.linear_fc1 = ColumnParallelLinear(dim, hidden, **kw)
+        self.linear_fc2 = RowParallelLinear(hidden, dim, **kw)
 
     def forward(self, x):
         return self.linear_fc2(self.linear_fc1(x, activation=self.activation))
@@ -232,23 +269,23 @@ class JointAttention(nn.Module):
     """Dual-stream attention: separate QKV / out projections for video and text tokens."""
 
     def __init__(self, dim: int, heads: int, head_dim: int, tp: int, eps: float, qkv_bias: bool = True,
-                 device=None, dtype=None):
+                 sequence_parallel: bool = False, device=None, dtype=None):
         super().__init__()
         kw = dict(device=device, dtype=dtype)
         self.heads_local, self.head_dim, self.eps = heads // tp, head_dim, eps
-        self.linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, **kw)
-        self.added_linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, **kw)
-        self.linear_proj = RowParallelLinear(dim, dim, tp=tp, **kw)
-        self.added_linear_proj = RowParallelLinear(dim, dim, tp=tp, **kw)
+        self.sequence_parallel = sp = sequence_parallel and tp > 1
+        self.linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, sequence_parallel=sp, **kw)
+        self.added_linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, sequence_parallel=sp, **kw)
+        self.linear_proj = RowParallelLinear(dim, dim, tp=tp, sequence_parallel=sp, **kw)
+        self.added_linear_proj = RowParallelLinear(dim, dim, tp=tp, sequence_parallel=sp, **kw)
         self.q_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
         self.k_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
         self.added_q_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
         self.added_k_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
 
     def forward(self, x, ctx, cos, sin, pad, kv_valid_len):
-        tpg = ps.get_tensor_model_parallel_group()
-        x = M.copy_to_tensor_model_parallel_region(x, tpg)
-        ctx = M.copy_to_tensor_model_parallel_region(ctx, tpg)
+        x = tp_region_input(x, self.sequence_parallel)
+        ctx = tp_region_input(ctx, self.sequence_parallel)
         if _use_fused(x, self.head_dim):
             return self._forward_fused(x, ctx, cos, sin, pad, kv_valid_len)
         if ps.get_context_parallel_world_size() == 1:
@@ -285,9 +322,8 @@ class JointAttention(nn.Module):
                                            self.added_linear_proj.weight, self.added_linear_proj.bias if tp == 1 else None,
                                            kv_len=kv_len)
         if tp > 1:
-            g = ps.get_tensor_model_parallel_group()
-            y = M.reduce_from_tensor_model_parallel_region(y, g) + self.linear_proj.bias
-            yt = M.reduce_from_tensor_model_parallel_region(yt, g) + self.added_linear_proj.bias
+            y = tp_region_output(y, self.sequence_parallel) + self.linear_proj.bias
+            yt = tp_region_output(yt, self.sequence_parallel) + self.added_linear_proj.bias
         return y, yt
 
 
@@ -295,16 +331,17 @@ class SingleAttention(nn.Module):
     """Single-stream attention: one QKV over ``cat(video, text)``; no output projection."""
 
     def __init__(self, dim: int, heads: int, head_dim: int, tp: int, eps: float, qkv_bias: bool = True,
-                 device=None, dtype=None):
+                 sequence_parallel: bool = False, device=None, dtype=None):
         super().__init__()
         kw = dict(device=device, dtype=dtype)
         self.heads_local, self.head_dim, self.eps = heads // tp, head_dim, eps
-        self.linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, **kw)
+        self.linear_qkv = ColumnParallelLinear(dim, 3 * dim, bias=qkv_bias, tp=tp, sequence_parallel=sequence_parallel, **kw)
         self.q_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
         self.k_layernorm = RMSNorm(head_dim, eps, tp > 1, **kw)
 
-    def forward(self, h, text_len, cos, sin, pad, kv_valid_len):
-        h = M.copy_to_tensor_model_parallel_region(h, ps.get_tensor_model_parallel_group())
+    def forward(self, h, text_len, cos, sin, pad, kv_valid_len, in_region: bool = False):
+        if not in_region:
+            h = M.copy_to_tensor_model_parallel_region(h, ps.get_tensor_model_parallel_group())
         s = h.shape[1] - text_len
         q, k, v = ops.qkv_projection(h, self.linear_qkv.weight, self.linear_qkv.bias, self.q_layernorm.weight,
                                      self.k_layernorm.weight, cos, sin, self.heads_local, self.eps, rope_len=s)
@@ -326,12 +363,13 @@ class HunyuanDiTLayer(nn.Module):
         kw = dict(device=device, dtype=dtype)
         H = cfg.hidden_size
         self.eps = cfg.layernorm_epsilon
-        self.norm1 = AdaLNModulation(H, 6, tp, **kw)
-        self.norm1_context = AdaLNModulation(H, 6, tp, **kw)
+        sp = bool(getattr(cfg, "sequence_parallel", False)) and tp > 1
+        self.norm1 = AdaLNModulation(H, 6, tp, sp, **kw)
+        self.norm1_context = AdaLNModulation(H, 6, tp, sp, **kw)
         self.self_attention = JointAttention(H, cfg.num_attention_heads, cfg.attention_head_dim, tp, self.eps,
-                                             cfg.add_qkv_bias, **kw)
-        self.mlp = ParallelMLP(H, cfg.mlp_hidden, cfg.dual_mlp_activation, tp, **kw)
-        self.ff_context = ParallelMLP(H, cfg.mlp_hidden, cfg.dual_mlp_activation, tp, **kw)
+                                             cfg.add_qkv_bias, sp, **kw)
+        self.mlp = ParallelMLP(H, cfg.mlp_hidden, cfg.dual_mlp_activation, tp, sp, **kw)
+        self.ff_context = ParallelMLP(H, cfg.mlp_hidden, cfg.dual_mlp_activation, tp, sp, **kw)
 
     def forward(self, x, ctx, temb, cos, sin, pad: Optional[SeqPad] = None, kv_valid_len: Optional[int] = None):
         shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.norm1(temb)
@@ -362,35 +400,45 @@ class HunyuanSingleDiTLayer(nn.Module):
         H = cfg.hidden_size
         self.eps = cfg.layernorm_epsilon
         self.activation = cfg.single_mlp_activation
-        self.norm = AdaLNModulation(H, 3, tp, **kw)
-        self.proj_mlp = ColumnParallelLinear(H, cfg.mlp_hidden, tp=tp, **kw)
+        self.sequence_parallel = sp = bool(getattr(cfg, "sequence_parallel", False)) and tp > 1
+        self.norm = AdaLNModulation(H, 3, tp, sp, **kw)
+        self.proj_mlp = ColumnParallelLinear(H, cfg.mlp_hidden, tp=tp, sequence_parallel=sp, **kw)
         self.self_attention = SingleAttention(H, cfg.num_attention_heads, cfg.attention_head_dim, tp, self.eps,
-                                              cfg.add_qkv_bias, **kw)
-        self.proj_out = RowParallelLinear(H + cfg.mlp_hidden, H, tp=tp, input_partitions=(H, cfg.mlp_hidden), **kw)
+                                              cfg.add_qkv_bias, sp, **kw)
+        self.proj_out = RowParallelLinear(H + cfg.mlp_hidden, H, tp=tp, input_partitions=(H, cfg.mlp_hidden),
+                                          sequence_parallel=sp, **kw)
 
     def forward(self, x, ctx, temb, cos, sin, pad: Optional[SeqPad] = None, kv_valid_len: Optional[int] = None):
-        T = ctx.shape[1]
+        T_own = ctx.shape[1]                       # text rows held by this rank (all of them without sequence parallelism)
         h = torch.cat([x, ctx], dim=1)
         shift, scale, gate = self.norm(temb)
         hn = ops.layernorm_modulate(h, scale, shift, self.eps)
-        mlp = self.proj_mlp(hn, activation=self.activation)
+        sp = self.sequence_parallel
+        T, splits = T_own, None
+        if sp:
+            # video and text token blocks are gathered separately so that the result is [all video | all text]
+            hn = torch.cat([tp_region_input(hn[:, :-T_own], True), tp_region_input(hn[:, -T_own:], True)], dim=1)
+            T = T_own * self.proj_out.tp
+            splits = (hn.shape[1] - T, T)
+        mlp = self.proj_mlp(hn, activation=self.activation, in_region=sp)
         if _use_fused(hn, self.self_attention.head_dim):
-            proj = self._attention_and_projection_fused(hn, mlp, T, cos, sin, pad, kv_valid_len)
+            proj = self._attention_and_projection_fused(hn, mlp, T, cos, sin, pad, kv_valid_len, in_region=sp)
         else:
-            attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len)
+            attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len, in_region=sp)
             merged = torch.cat([torch.cat([attn, c_attn], dim=1), mlp], dim=2)
-            proj = self.proj_out(merged)
+            proj = self.proj_out(merged, row_splits=splits)
         h = ops.gate_residual(h, proj, gate)
-        return h[:, :-T], h[:, -T:]
+        return h[:, :-T_own], h[:, -T_own:]
 
-    def _attention_and_projection_fused(self, hn, mlp, T, cos, sin, pad, kv_valid_len):
+    def _attention_and_projection_fused(self, hn, mlp, T, cos, sin, pad, kv_valid_len, in_region: bool = False):
         """Single-stream block with both Ulysses all-to-alls fused: the QKV epilogue scatters heads to their owners and
         the merged projection gathers them back per K block, taking the MLP half of its input from local memory."""
         from ...ops import fused_comm as FC
         sa = self.self_attention
         s = hn.shape[1] - T
         ws = _workspace(sa.heads_local, s, T)
-        hn = M.copy_to_tensor_model_parallel_region(hn, ps.get_tensor_model_parallel_group())
+        if not in_region:
+            hn = M.copy_to_tensor_model_parallel_region(hn, ps.get_tensor_model_parallel_group())
         xv, xt = hn[:, :s], hn[:, s:]
         w, b = sa.linear_qkv.weight, sa.linear_qkv.bias
         q, k, v = FC.fused_qkv_a2a(ws, xv, w, b, sa.q_layernorm.weight, sa.k_layernorm.weight, cos, sin,
@@ -401,7 +449,7 @@ class HunyuanSingleDiTLayer(nn.Module):
                                            kv_len=_fused_kv_len(ws, pad, kv_valid_len))
         proj = torch.cat([y, yt], dim=1)
         if tp > 1:
-            proj = M.reduce_from_tensor_model_parallel_region(proj, ps.get_tensor_model_parallel_group()) + self.proj_out.bias
+            proj = tp_region_output(proj, self.sequence_parallel, (s, T) if self.sequence_parallel else None) + self.proj_out.bias
         return proj
 
 

@@ -43,6 +43,8 @@ class HunyuanParams:
     recompute_granularity: Optional[str] = None      # None | "full" | "selective"
     recompute_method: str = "block"                  # "block" | "uniform"
     recompute_num_layers: Optional[int] = None       # None = every block (reference behaviour)
+    sequence_parallel: bool = False                  # shard the residual stream's tokens over tensor-parallel ranks
+    sequence_parallel_row_multiple: int = 1          # token blocks are padded to a multiple of this (128 for the fused TP kernels)
     recompute_save_attention: bool = False           # keep attention (out, lse) so the recompute pass skips that kernel
     fused_kernels: bool = True
     init_method_std: float = 0.006

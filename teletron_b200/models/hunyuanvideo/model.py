@@ -152,15 +152,29 @@ class HunyuanVideoTransformer3DModel(nn.Module):
         cp = ps.get_context_parallel_world_size()
         cp_group = ps.get_context_parallel_group()
         pad = None
+        sp = bool(cfg.sequence_parallel) and self.tp > 1
+        tp_group = ps.get_tensor_model_parallel_group()
+        if sp and ctx.shape[1] % self.tp:
+            raise ValueError(f"sequence parallelism needs the text length {ctx.shape[1]} divisible by tp = {self.tp}")
+        if sp and cp == 1 and x.shape[1] % self.tp:
+            raise ValueError(f"sequence parallelism needs the video token count {x.shape[1]} divisible by tp = {self.tp}")
         if cp > 1:
-            pad = SeqPad.for_length(x.shape[1], cp)
+            # with sequence parallelism each context-parallel chunk is cut once more into tp token blocks
+            pad = SeqPad.for_length(x.shape[1], cp * self.tp * cfg.sequence_parallel_row_multiple if sp else cp)
             x = M.split_forward_gather_backward(pad.add(x, 1), cp_group, dim=1, grad_scale="down")
             cos = M.split_forward_gather_backward(pad.add(cos, 0), cp_group, dim=0, grad_scale="down")
             sin = M.split_forward_gather_backward(pad.add(sin, 0), cp_group, dim=0, grad_scale="down")
 
+        if sp:
+            x = M.scatter_to_sequence_parallel_region(x, tp_group, dim=1)
+            ctx = M.scatter_to_sequence_parallel_region(ctx, tp_group, dim=1)
+
         x, ctx = self._run_blocks(self.transformer_blocks, x, ctx, temb, cos, sin, pad, kv_valid_len)
         x, ctx = self._run_blocks(self.single_transformer_blocks, x, ctx, temb, cos, sin, pad, kv_valid_len)
 
+        if sp:
+            # everything after the blocks is replicated over TP: every rank holds the full gradient of the gathered rows
+            x = M.gather_forward_split_backward(x, tp_group, dim=1, grad_scale=None)
         if cp > 1:
             x = M.gather_forward_split_backward(x, cp_group, dim=1, grad_scale="up")
             x = pad.remove(x, 1)

@@ -239,3 +239,84 @@ def gather_from_tensor_model_parallel_region(x, group):
     if _size(group) == 1:
         return x
     return _GatherFromTP.apply(x, group)
+
+
+# ---------------------------------------------------------------------------------------------
+# Sequence parallelism over the tensor-parallel group: the residual stream is sharded along the
+# token dim between the column- and row-parallel linears (all-gather in, reduce-scatter out)
+# ---------------------------------------------------------------------------------------------
+
+def _reduce_scatter(x: torch.Tensor, group, dim: int) -> torch.Tensor:
+    """Sum over the group, keep this rank's chunk of ``dim``."""
+    n = _size(group)
+    if n == 1:
+        return x
+    if x.size(dim) % n:
+        raise ValueError(f"dim {dim} of size {x.size(dim)} is not divisible by {n}")
+    if dim != 0:
+        step = x.size(dim) // n
+        x = torch.cat(x.split(step, dim=dim), dim=0)        # chunk r of `dim` becomes row block r
+    x = x.contiguous()
+    out = torch.empty((x.size(0) // n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, x, group=group)
+    return out
+
+
+class _GatherSeqFwdReduceScatterBwd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        return _gather(x, group, dim, None)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter(g, ctx.group, ctx.dim), None, None
+
+
+class _ReduceScatterSeqFwdGatherBwd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        ctx.group, ctx.dim = group, dim
+        return _reduce_scatter(x, group, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather(g, ctx.group, ctx.dim, None), None, None
+
+
+class _GatherFromTPReduceGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _gather(x, group, x.dim() - 1, None)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter(g, ctx.group, g.dim() - 1), None
+
+
+def scatter_to_sequence_parallel_region(x, group, dim: int = 1):
+    """Keep this rank's token block; backward all-gathers the blocks' gradients."""
+    return split_forward_gather_backward(x, group, dim, grad_scale=None)
+
+
+def gather_from_sequence_parallel_region(x, group, dim: int = 1):
+    """All-gather token blocks (input of a column-parallel linear); backward reduce-scatters."""
+    if _size(group) == 1:
+        return x
+    return _GatherSeqFwdReduceScatterBwd.apply(x, group, dim)
+
+
+def reduce_scatter_to_sequence_parallel_region(x, group, dim: int = 1):
+    """Sum the partial outputs of a row-parallel linear and keep this rank's token block."""
+    if _size(group) == 1:
+        return x
+    return _ReduceScatterSeqFwdGatherBwd.apply(x, group, dim)
+
+
+def gather_from_tensor_model_parallel_region_reduce_grad(x, group):
+    """All-gather along the last dim; backward sums the gradients over the group before the split.  For a replicated
+    result (modulation vectors) whose consumers each see only part of the tokens."""
+    if _size(group) == 1:
+        return x
+    return _GatherFromTPReduceGrad.apply(x, group)

@@ -7,6 +7,10 @@ import torch
 from dist_utils import run_distributed
 
 
+# tp * cp = 4 needs at least 4 heads: 4 x 32 instead of the tiny model's 2 x 64
+HEADS4 = dict(num_attention_heads=4, attention_head_dim=32, rope_axes_dim=(8, 12, 12))
+
+
 def _make_batch():
     g = torch.Generator().manual_seed(7)
     return dict(latents=torch.randn(1, 16, 3, 8, 8, generator=g), prompt_embeds=torch.randn(1, 16, 64, generator=g),
@@ -28,13 +32,13 @@ def _full_grads(pipe, tp, tp_group):
     return out
 
 
-def _run(rank, world, tp, cp, recompute, frames):
+def _run(rank, world, tp, cp, recompute, frames, sp=False, heads4=False):
     import torch.distributed as dist
     from teletron_b200.models.hunyuanvideo import FlowConfig, HunyuanPipeline, tiny_config
     from teletron_b200.parallel import state as ps
     ps.initialize_model_parallel(tp, cp)
     torch.manual_seed(0)
-    cfg = tiny_config(recompute_granularity="full" if recompute else None)
+    cfg = tiny_config(recompute_granularity="full" if recompute else None, sequence_parallel=sp, **(HEADS4 if heads4 else {}))
     pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"))
     batch = _make_batch()
     if frames != 3:
@@ -53,12 +57,12 @@ def _run(rank, world, tp, cp, recompute, frames):
     return float(loss.detach()), {k: v for k, v in grads.items()}
 
 
-def _single(recompute=False, frames=3):
+def _single(recompute=False, frames=3, heads4=False):
     from teletron_b200.models.hunyuanvideo import FlowConfig, HunyuanPipeline, tiny_config
     from teletron_b200.parallel import state as ps
     ps.destroy_model_parallel()
     torch.manual_seed(0)
-    pipe = HunyuanPipeline(tiny_config(), FlowConfig(model_type="t2v"))
+    pipe = HunyuanPipeline(tiny_config(**(HEADS4 if heads4 else {})), FlowConfig(model_type="t2v"))
     batch = _make_batch()
     if frames != 3:
         g = torch.Generator().manual_seed(7)
@@ -73,6 +77,19 @@ def test_layout_matches_single_process(tp, cp, recompute, frames):
     # frames=5 with a 6x6 latent gives 45 video tokens: not divisible by cp=2 -> exercises the padding path
     ref_loss, ref_grads = _single(frames=frames)
     results = run_distributed(_run, 2, tp, cp, recompute, frames)
+    for loss, grads in results:
+        assert abs(loss - ref_loss) < 1e-5 * max(1.0, abs(ref_loss))
+        for n, g in ref_grads.items():
+            torch.testing.assert_close(grads[n], g, rtol=2e-4, atol=2e-6, msg=lambda m, n=n: f"{n}: {m}")
+
+
+@pytest.mark.parametrize("world,tp,cp,recompute,frames", [(2, 2, 1, False, 3), (2, 2, 1, True, 3), (4, 2, 2, False, 3),
+                                                          (4, 2, 2, False, 5)])
+def test_sequence_parallel_matches_single_process(world, tp, cp, recompute, frames):
+    """Token-sharded residual stream over TP (all-gather into column-parallel, reduce-scatter out of row-parallel
+    linears): same loss and gradients as one process.  frames=5 gives 45 video tokens, padded to a multiple of cp*tp."""
+    ref_loss, ref_grads = _single(frames=frames, heads4=world == 4)
+    results = run_distributed(_run, world, tp, cp, recompute, frames, True, world == 4)
     for loss, grads in results:
         assert abs(loss - ref_loss) < 1e-5 * max(1.0, abs(ref_loss))
         for n, g in ref_grads.items():
