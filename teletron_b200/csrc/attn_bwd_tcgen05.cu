@@ -2,22 +2,29 @@
 // atomics-free, deterministic kernels built from one template:
 //
 //   KV-stationary (dK, dV): a CTA owns 128 keys (K, V tiles resident in shared memory) and streams the
-//     queries in chunks of 64 rows (Q, dO).   T1 = K Q^T = S^T,  T2 = V dO^T = dP^T,
+//     queries in chunks of 128 rows (Q, dO).   T1 = K Q^T = S^T,  T2 = V dO^T = dP^T,
 //     P^T = exp2(S^T * c - lse[q]),  dS^T = P^T * (dP^T - delta[q]),  dV += P^T dO,  dK += dS^T Q.
-//   Q-stationary (dQ): a CTA owns 128 queries (Q, dO resident) and streams the keys in chunks of 64
+//   Q-stationary (dQ): a CTA owns 128 queries (Q, dO resident) and streams the keys in chunks of 128
 //     (K, V).   T1 = Q K^T = S,  T2 = dO V^T = dP,  dS = exp2(S * c - lse[row]) * (dP - delta[row]),
 //     dQ += dS K.
 //
-// Both run the same pipeline.  Stationary operands [128 x 128] are loaded once; streamed chunks
-// [64 x 128] x 2 go through a 4-stage TMA ring.  T1 / T2 (128 x 64 fp32 each) are double buffered in
-// tensor memory, so the tensor core computes the next chunk's T products and the previous chunk's
-// accumulator updates while the eight softmax warps (one stationary row x 32 streamed columns per thread) turn the current
-// T1 / T2 into bf16 P / dS, written back over T1 / T2 in tensor memory and consumed from there as the
-// A operand of the accumulator MMAs.  The streamed chunk is used twice from the same shared-memory bytes:
-// as a K-major B operand for the T products and as an MN-major B operand for the accumulator updates.
+// Both run the same pipeline.  Stationary operands [128 x 128] are loaded once; streamed chunks are 128 rows
+// ([128 x 128] x 2 operands per stage, two TMA stages).  Chunks of 128 keep every MMA at N = 128: an N = 64
+// instruction was measured to take as long as an N = 128 one on this part, so 64-row chunks ran the T products at
+// half rate.  T1 and T2 are single-buffered in tensor memory and the overlap comes from the order of issue:
 //
-//   TMEM columns: [0,64) T1 buf0 (P0 aliases [0,32)), [64,128) T2 buf0 (dS0 aliases [64,96)),
-//                 [128,192) T1 buf1, [192,256) T2 buf1, [256,384) accumulator 1, [384,512) accumulator 2.
+//   tensor core:  ... dV(c) | S(c+1) | dK(c) | dP(c+1) | dV(c+1) | S(c+2) ...
+//   softmax:      ... dS(c) ........ | P(c+1) .......... | dS(c+1) ........ ...
+//
+// S(c+1) may overwrite T1 as soon as dV(c) has consumed P(c); dP(c+1) may overwrite T2 as soon as dK(c) has
+// consumed dS(c); the tensor core executes in issue order, so these hazards need no extra barrier.  The eight softmax
+// warps (one stationary row x 64 streamed columns per thread) write bf16 P / dS back over T1 / T2, consumed from
+// tensor memory as the A operand of the accumulator MMAs; P stays packed in registers between the two passes.  The
+// streamed chunk is used twice from the same shared-memory bytes: as a K-major B operand for the T products and as
+// an MN-major B operand for the accumulator updates.
+//
+//   TMEM columns: [0,128) T1 = S (P aliases [0,32) and [64,96)), [128,256) T2 = dP (dS aliases [128,160) and
+//                 [192,224)), [256,384) accumulator 1, [384,512) accumulator 2.
 //
 // q, k, v, dq, dk, dv: [B*H, S, 128] bf16 head-major; dout: [B, S, H*128] bf16 token-major;
 // lse, delta: [B*H, pitch] fp32 (delta = rowsum(dO * O), computed by the preprocess kernel below).
@@ -32,15 +39,13 @@ using namespace sm100;
 
 constexpr int D = 128;
 constexpr int BS = 128;            // stationary rows
-constexpr int BC = 64;             // streamed rows per chunk
-constexpr int kStages = 4;
+constexpr int BC = 128;            // streamed rows per chunk
+constexpr int kStages = 2;
 constexpr int kThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2-9 softmax / epilogue (two warpgroups)
-constexpr int kStatSlab = BS * 128;        // [128 x 64] slab: 16 KB
-constexpr int kStatTile = 2 * kStatSlab;   // [128 x 128]: 32 KB
-constexpr int kChunkSlab = BC * 128;       // [64 x 64] slab: 8 KB
-constexpr int kChunkTile = 2 * kChunkSlab; // [64 x 128]: 16 KB
-constexpr int kStageBytes = 2 * kChunkTile;   // two streamed operands per stage: 32 KB
-constexpr int kSmemBytes = 2 * kStatTile + kStages * kStageBytes + 1024 /* stats */ + 256 /* barriers */ + 1024;
+constexpr int kSlab = 128 * 128;           // [128 rows x 64 columns] bf16 slab, 128-byte rows: 16 KB
+constexpr int kTile = 2 * kSlab;           // [128 x 128]: 32 KB
+constexpr int kStageBytes = 2 * kTile;     // two streamed operands per stage: 64 KB
+constexpr int kSmemBytes = 2 * kTile + kStages * kStageBytes + 1024 /* stats */ + 256 /* barriers */ + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -85,15 +90,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA1 = base;                       // stationary operand 1 (K or Q)
-    const uint32_t sA2 = base + kStatTile;           // stationary operand 2 (V or dO)
-    const uint32_t sRing = base + 2 * kStatTile;     // stage: [B1 chunk (Q or K) | B2 chunk (dO or V)]
-    const uint32_t bars = base + 2 * kStatTile + kStages * kStageBytes + 1024;
+    const uint32_t sA2 = base + kTile;               // stationary operand 2 (V or dO)
+    const uint32_t sRing = base + 2 * kTile;         // stage: [B1 chunk (Q or K) | B2 chunk (dO or V)]
+    const uint32_t bars = base + 2 * kTile + kStages * kStageBytes + 1024;
     const uint32_t a_full = bars;
     auto b_full = [&](int s) { return bars + 8u * (1 + s); };
     auto b_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
-    auto t_full = [&](int u) { return bars + 8u * (1 + 2 * kStages + u); };
-    auto p_full = [&](int u) { return bars + 8u * (3 + 2 * kStages + u); };
-    const uint32_t acc_final = bars + 8u * (5 + 2 * kStages);
+    const uint32_t s_full = bars + 8u * (1 + 2 * kStages);     // T1 = S holds this chunk's scores
+    const uint32_t dp_full = s_full + 8u;                      // T2 = dP holds this chunk's products
+    const uint32_t p_ready = s_full + 16u;                     // S has been read (and P written back, KV-stationary)
+    const uint32_t ds_ready = s_full + 24u;                    // dS has been written over dP
+    const uint32_t acc_final = s_full + 32u;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
@@ -109,10 +116,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             mbar_init(b_full(s), 1);
             mbar_init(b_empty(s), 1);
         }
-        for (int u = 0; u < 2; ++u) {
-            mbar_init(t_full(u), 1);
-            mbar_init(p_full(u), 8);
-        }
+        mbar_init(s_full, 1);
+        mbar_init(dp_full, 1);
+        mbar_init(p_ready, 8);
+        mbar_init(ds_ready, 8);
         mbar_init(acc_final, 1);
         fence_barrier_init();
         fence_proxy_async();
@@ -125,19 +132,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
+    constexpr uint32_t kT1 = 0, kT2 = 128, kAcc1 = 256, kAcc2 = 384;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_arrive_expect_tx(a_full, 2 * kStatTile);
+            mbar_arrive_expect_tx(a_full, 2 * kTile);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 if (KVS) {
-                    tma_load_3d(sA1 + h * kStatSlab, &tmK, a_full, h * 64, r0, bh);
-                    tma_load_3d(sA2 + h * kStatSlab, &tmV, a_full, h * 64, r0, bh);
+                    tma_load_3d(sA1 + h * kSlab, &tmK, a_full, h * 64, r0, bh);
+                    tma_load_3d(sA2 + h * kSlab, &tmV, a_full, h * 64, r0, bh);
                 } else {
-                    tma_load_3d(sA1 + h * kStatSlab, &tmQ, a_full, h * 64, r0, bh);
-                    tma_load_4d(sA2 + h * kStatSlab, &tmDO, a_full, h * 64, head, r0, b);
+                    tma_load_3d(sA1 + h * kSlab, &tmQ, a_full, h * 64, r0, bh);
+                    tma_load_4d(sA2 + h * kSlab, &tmDO, a_full, h * 64, head, r0, b);
                 }
             }
             for (int c = 0; c < n_chunks; ++c) {
@@ -149,11 +157,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (KVS) {
-                        tma_load_3d(dst + h * kChunkSlab, &tmQ, b_full(s), h * 64, c * BC, bh);
-                        tma_load_4d(dst + kChunkTile + h * kChunkSlab, &tmDO, b_full(s), h * 64, head, c * BC, b);
+                        tma_load_3d(dst + h * kSlab, &tmQ, b_full(s), h * 64, c * BC, bh);
+                        tma_load_4d(dst + kTile + h * kSlab, &tmDO, b_full(s), h * 64, head, c * BC, b);
                     } else {
-                        tma_load_3d(dst + h * kChunkSlab, &tmK, b_full(s), h * 64, c * BC, bh);
-                        tma_load_3d(dst + kChunkTile + h * kChunkSlab, &tmV, b_full(s), h * 64, c * BC, bh);
+                        tma_load_3d(dst + h * kSlab, &tmK, b_full(s), h * 64, c * BC, bh);
+                        tma_load_3d(dst + kTile + h * kSlab, &tmV, b_full(s), h * 64, c * BC, bh);
                     }
                 }
             }
@@ -161,68 +169,62 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_t = idesc_bf16(BS, BC, false, false);   // T = A B^T, both K-major, N = 64
-            constexpr uint32_t idesc_a = idesc_bf16(BS, D, false, true);     // acc += P B, B MN-major, N = 128
-            auto issue_t = [&](int c) {
-                const int u = c & 1;
-                const uint32_t sb = sRing + (c % kStages) * kStageBytes;
+            constexpr uint32_t idesc_t = idesc_bf16(BS, BC, false, false);   // T = A B^T, both K-major
+            constexpr uint32_t idesc_a = idesc_bf16(BS, D, false, true);     // acc += P B, B MN-major
+            // T[128 x 128] = stationary (K-major) x chunk^T (K-major): eight K = 16 steps over the head dim
+            auto issue_t = [&](uint32_t t_col, uint32_t sa, uint32_t sb) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t oa = (kk >> 2) * kStatSlab + (kk & 3) * 32;
-                    const uint32_t ob = (kk >> 2) * kChunkSlab + (kk & 3) * 32;
-                    umma_bf16_ss(tmem + u * 128, smem_desc_sw128(sA1 + oa, 16, 1024), smem_desc_sw128(sb + ob, 16, 1024),
-                                 idesc_t, kk ? 1u : 0u);
+                    const uint32_t o = (kk >> 2) * kSlab + (kk & 3) * 32;
+                    umma_bf16_ss(tmem + t_col, smem_desc_sw128(sa + o, 16, 1024), smem_desc_sw128(sb + o, 16, 1024), idesc_t,
+                                 kk ? 1u : 0u);
                 }
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t oa = (kk >> 2) * kStatSlab + (kk & 3) * 32;
-                    const uint32_t ob = (kk >> 2) * kChunkSlab + (kk & 3) * 32;
-                    umma_bf16_ss(tmem + u * 128 + 64, smem_desc_sw128(sA2 + oa, 16, 1024),
-                                 smem_desc_sw128(sb + kChunkTile + ob, 16, 1024), idesc_t, kk ? 1u : 0u);
-                }
-                umma_commit(t_full(u));
             };
-            auto issue_acc = [&](int c) {
-                const int u = c & 1;
-                const uint32_t sb = sRing + (c % kStages) * kStageBytes;
-                if (KVS) {
-                    // dV += P^T dO  (P at T1 columns, B = dO chunk)
-#pragma unroll
-                    for (int kk = 0; kk < BC / 16; ++kk)
-                        umma_bf16_ts(tmem + 256, tmem + u * 128 + kk * 8,
-                                     smem_desc_sw128(sb + kChunkTile + kk * 2048, kChunkSlab, 1024), idesc_a, (c | kk) ? 1u : 0u);
-                }
-                // dK += dS^T Q   /   dQ += dS K   (dS at T2 columns, B = first streamed operand)
+            // acc[128 x 128] += A (bf16 pairs in tensor memory, 128 x 128 chunk rows) x chunk (MN-major B)
+            auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t sb, bool first) {
 #pragma unroll
                 for (int kk = 0; kk < BC / 16; ++kk)
-                    umma_bf16_ts(tmem + (KVS ? 384 : 256), tmem + u * 128 + 64 + kk * 8,
-                                 smem_desc_sw128(sb + kk * 2048, kChunkSlab, 1024), idesc_a, (c | kk) ? 1u : 0u);
-                umma_commit(b_empty(c % kStages));
+                    umma_bf16_ts(tmem + acc_col, tmem + a_col + (kk >> 2) * 64 + (kk & 3) * 8,
+                                 smem_desc_sw128(sb + kk * 2048, kSlab, 1024), idesc_a, (first && kk == 0) ? 0u : 1u);
             };
             if (!mbar_wait(a_full, 0, &abort_flag)) goto done;
-            for (int c = 0; c < 2 && c < n_chunks; ++c) {
-                if (!mbar_wait(b_full(c % kStages), 0, &abort_flag)) goto done;
-                tc_fence_after();
-                issue_t(c);
-            }
+            if (!mbar_wait(b_full(0), 0, &abort_flag)) goto done;
+            tc_fence_after();
+            issue_t(kT1, sA1, sRing);
+            umma_commit(s_full);
+            issue_t(kT2, sA2, sRing + kTile);
+            umma_commit(dp_full);
             for (int c = 0; c < n_chunks; ++c) {
-                if (!mbar_wait(p_full(c & 1), (uint32_t)(c >> 1) & 1u, &abort_flag)) goto done;
+                const uint32_t par = (uint32_t)c & 1u;
+                const uint32_t sb = sRing + (c % kStages) * kStageBytes;
+                const bool more = c + 1 < n_chunks;
+                const uint32_t sb_next = sRing + ((c + 1) % kStages) * kStageBytes;
+                if (!mbar_wait(p_ready, par, &abort_flag)) goto done;
                 tc_fence_after();
-                issue_acc(c);
-                if (c + 2 < n_chunks) {
-                    const int c2 = c + 2;
-                    if (!mbar_wait(b_full(c2 % kStages), (uint32_t)(c2 / kStages) & 1u, &abort_flag)) goto done;
+                if (KVS) issue_acc(kAcc1, kT1, sb + kTile, c == 0);          // dV += P^T dO
+                if (more) {
+                    if (!mbar_wait(b_full((c + 1) % kStages), (uint32_t)((c + 1) / kStages) & 1u, &abort_flag)) goto done;
                     tc_fence_after();
-                    issue_t(c2);
+                    issue_t(kT1, sA1, sb_next);                              // next chunk's scores: overlaps the dS pass
+                    umma_commit(s_full);
+                }
+                if (!mbar_wait(ds_ready, par, &abort_flag)) goto done;
+                tc_fence_after();
+                issue_acc(KVS ? kAcc2 : kAcc1, kT2, sb, c == 0);             // dK += dS^T Q   /   dQ += dS K
+                umma_commit(b_empty(c % kStages));
+                if (more) {
+                    issue_t(kT2, sA2, sb_next + kTile);                      // next chunk's dP: overlaps its P pass
+                    umma_commit(dp_full);
                 }
             }
             umma_commit(acc_final);
         }
     } else {
         // ------------------------------------------------------------ softmax / dS
-        // Two warpgroups share every chunk: a thread owns one stationary row and 32 of the chunk's 64 streamed
-        // columns (warpgroup 0: columns [0, 32), warpgroup 1: [32, 64)), so two warps per scheduler hide each
-        // other's tcgen05.ld / exp2 latency.
+        // Two warpgroups share every chunk: a thread owns one stationary row and 64 of the chunk's 128 streamed
+        // rows (columns of T1 / T2; warpgroup 0: [0, 64), warpgroup 1: [64, 128)).  Each chunk has two passes:
+        // P from the scores (runs while the tensor core forms dP), then dS from dP (runs while it forms the
+        // next chunk's scores and, KV-stationary, dV).
         const int half = (warp - 2) >> 2;
         const int quad = warp & 3;
         const int srow = quad * 32 + lane;                 // row within the stationary tile
@@ -238,41 +240,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             my_lse = row_live ? p.lse[(long)bh * p.pitch + row] * kLog2e : INFINITY;
             my_delta = row_live ? p.delta[(long)bh * p.pitch + row] : 0.f;
         }
+        const uint32_t t1 = tmem + lane_sel + kT1 + half * 64, t2 = tmem + lane_sel + kT2 + half * 64;
         for (int c = 0; c < n_chunks; ++c) {
-            const int u = c & 1;
-            const int col0 = c * BC;
-            // KV-stationary: the chunk's 64 queries each have their own lse / delta; every thread reads them
-            // straight from global memory (same addresses across the warp, so each load is one broadcast)
+            const uint32_t par = (uint32_t)c & 1u;
+            const int col0 = c * BC + half * 64;           // first streamed row of this thread's 64 columns
+            // KV-stationary: the streamed queries each have their own lse / delta; every thread reads them straight
+            // from global memory (same addresses across the warp, so each load is one broadcast).  The statistics
+            // rows are `pitch` long (a multiple of 64): a 64-column group past the end has no live query.
+            const bool cols_ok = !KVS || col0 < p.pitch;
             const float4* lse4 = reinterpret_cast<const float4*>(p.lse + (long)bh * p.pitch + col0);
             const float4* del4 = reinterpret_cast<const float4*>(p.delta + (long)bh * p.pitch + col0);
-            if (!mbar_wait(t_full(u), (uint32_t)(c >> 1) & 1u, &abort_flag)) goto done;
+            uint32_t pk[32];
+            if (!mbar_wait(s_full, par, &abort_flag)) goto done;
             tc_fence_after();
-            const uint32_t t1 = tmem + lane_sel + u * 128, t2 = t1 + 64;
-            uint32_t pk[16], dk[16];
-            {
-                uint32_t a[32], g[32];
-                tmem_ld_32x32(t1 + half * 32, a);
-                tmem_ld_32x32(t2 + half * 32, g);
-                tmem_ld_wait();
-                float4 lq[8], dq4[8];
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                uint32_t a[32];
+                tmem_ld_32x32(t1 + pass * 32, a);
+                float4 lq[8];
                 if (KVS) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        lq[i] = __ldg(lse4 + half * 8 + i);
-                        dq4[i] = __ldg(del4 + half * 8 + i);
-                    }
+                    for (int i = 0; i < 8; ++i)
+                        lq[i] = cols_ok ? __ldg(lse4 + pass * 8 + i) : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
                 }
+                tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const int cc = half * 32 + 2 * i;
-                    float2 l2, d2;
+                    float2 l2;
                     if (KVS) {
-                        const float4 lv = lq[i >> 1], dv = dq4[i >> 1];
+                        const float4 lv = lq[i >> 1];
                         l2 = (i & 1) ? make_float2(lv.z * kLog2e, lv.w * kLog2e) : make_float2(lv.x * kLog2e, lv.y * kLog2e);
-                        d2 = (i & 1) ? make_float2(dv.z, dv.w) : make_float2(dv.x, dv.y);
                     } else {
                         l2 = make_float2(my_lse, my_lse);
-                        d2 = make_float2(my_delta, my_delta);
                     }
                     const float2 x = __ffma2_rn(make_float2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1])),
                                                 make_float2(c_log2, c_log2), make_float2(-l2.x, -l2.y));
@@ -280,23 +279,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     if (KVS) {
                         if (!row_live) pr = make_float2(0.f, 0.f);
                     } else {
-                        if (col0 + cc >= p.kv_len) pr.x = 0.f;
-                        if (col0 + cc + 1 >= p.kv_len) pr.y = 0.f;
+                        const int cc = col0 + pass * 32 + 2 * i;
+                        if (cc >= p.kv_len) pr.x = 0.f;
+                        if (cc + 1 >= p.kv_len) pr.y = 0.f;
                     }
-                    const float2 dp = make_float2(__uint_as_float(g[2 * i]) - d2.x, __uint_as_float(g[2 * i + 1]) - d2.y);
-                    const float2 ds = __fmul2_rn(pr, dp);
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(pr.x, pr.y);
-                    const __nv_bfloat162 db = __floats2bfloat162_rn(ds.x, ds.y);
-                    pk[i] = *reinterpret_cast<const uint32_t*>(&pb);
-                    dk[i] = *reinterpret_cast<const uint32_t*>(&db);
+                    pk[pass * 16 + i] = *reinterpret_cast<const uint32_t*>(&pb);
                 }
             }
-            if (KVS) tmem_st_32x16(t1 + half * 16, pk);
-            tmem_st_32x16(t2 + half * 16, dk);
+            if (KVS) {
+                // bf16 pairs over the first 32 of the 64 columns this thread has just read
+                tmem_st_32x16(t1, pk);
+                tmem_st_32x16(t1 + 16, pk + 16);
+                tmem_st_wait();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+
+            if (!mbar_wait(dp_full, par, &abort_flag)) goto done;
+            tc_fence_after();
+            uint32_t dk[32];
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                uint32_t g[32];
+                tmem_ld_32x32(t2 + pass * 32, g);
+                float4 dq4[8];
+                if (KVS) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dq4[i] = cols_ok ? __ldg(del4 + pass * 8 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float2 d2;
+                    if (KVS) {
+                        const float4 dv = dq4[i >> 1];
+                        d2 = (i & 1) ? make_float2(dv.z, dv.w) : make_float2(dv.x, dv.y);
+                    } else {
+                        d2 = make_float2(my_delta, my_delta);
+                    }
+                    const float2 pr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[pass * 16 + i]));
+                    const float2 dp = make_float2(__uint_as_float(g[2 * i]) - d2.x, __uint_as_float(g[2 * i + 1]) - d2.y);
+                    const float2 ds = __fmul2_rn(pr, dp);
+                    const __nv_bfloat162 db = __floats2bfloat162_rn(ds.x, ds.y);
+                    dk[pass * 16 + i] = *reinterpret_cast<const uint32_t*>(&db);
+                }
+            }
+            tmem_st_32x16(t2, dk);
+            tmem_st_32x16(t2 + 16, dk + 16);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(u));
+            if (lane == 0) mbar_arrive(ds_ready);
         }
         // ------------------------------------------------------------ epilogue
         if (!mbar_wait(acc_final, 0, &abort_flag)) goto done;
@@ -308,7 +344,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             __nv_bfloat16* dst = (which == 0 ? p.out1 : p.out2) + orow;
             // dV is unscaled; dK and dQ carry the softmax scale
             const float mul = (KVS && which == 0) ? 1.f : p.scale;
-            const uint32_t tacc = tmem + lane_sel + 256 + which * 128;
+            const uint32_t tacc = tmem + lane_sel + kAcc1 + which * 128;
 #pragma unroll 1
             for (int cch = half * 2; cch < half * 2 + 2; ++cch) {      // each warpgroup stores half of the columns
                 uint32_t r[32];
@@ -351,17 +387,12 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     if (pitch < S || (pitch & 63) || ((uintptr_t)lse & 15) || ((uintptr_t)delta & 15)) return TT_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const uint64_t BH = (uint64_t)B * H;
-    CUtensorMap tq_s, tk_s, tv_s, tdo_s;     // 128-row boxes (stationary operands)
-    CUtensorMap tq_c, tk_c, tv_c, tdo_c;     // 64-row boxes (streamed chunks)
+    CUtensorMap tq_s, tk_s, tv_s, tdo_s;     // 128-row x 64-column boxes (stationary operands and streamed chunks)
     int rc;
     if ((rc = tt_make_tmap_3d(&tq_s, q, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_3d(&tk_s, k, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_3d(&tv_s, v, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_bshd(&tdo_s, dout, (uint64_t)B, (uint64_t)S, (uint64_t)H, BS)) != TT_OK) return rc;
-    if ((rc = tt_make_tmap_3d(&tq_c, q, BH, (uint64_t)S, D, D, (uint64_t)S * D, BC, 64)) != TT_OK) return rc;
-    if ((rc = tt_make_tmap_3d(&tk_c, k, BH, (uint64_t)S, D, D, (uint64_t)S * D, BC, 64)) != TT_OK) return rc;
-    if ((rc = tt_make_tmap_3d(&tv_c, v, BH, (uint64_t)S, D, D, (uint64_t)S * D, BC, 64)) != TT_OK) return rc;
-    if ((rc = tt_make_tmap_bshd(&tdo_c, dout, (uint64_t)B, (uint64_t)S, (uint64_t)H, BC)) != TT_OK) return rc;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -387,12 +418,12 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     // dK, dV: stationary keys (K, V resident), streamed queries (Q, dO)
     p.out1 = (__nv_bfloat16*)dv;
     p.out2 = (__nv_bfloat16*)dk;
-    attn_bwd_kernel<true><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_c, tk_s, tv_s, tdo_c, p);
+    attn_bwd_kernel<true><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
     TT_CHECK_LAUNCH();
     // dQ: stationary queries (Q, dO resident), streamed keys (K, V)
     p.out1 = (__nv_bfloat16*)dq;
     p.out2 = nullptr;
-    attn_bwd_kernel<false><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_c, tv_c, tdo_s, p);
+    attn_bwd_kernel<false><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }

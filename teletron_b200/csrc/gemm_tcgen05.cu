@@ -686,6 +686,65 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
                      : dispatch<256>(false, b_mn != 0, 0, tmA, tmB, p, sms, st);
 }
 
+// Tensor-parallel all-gather -> GEMM with the epilogues of the plain GEMM: C[n * seg_rows, N] = epi(gather_r(A_r) op(B) + bias).
+//   a_ptrs[r]: rank r's [seg_rows, K] row block (peer memory); stage [n * seg_rows, K]: local buffer that receives the
+//   gathered operand (filled by the kernel's copier warps, one crossing of NVLink per remote row block) and stays valid
+//   after the call, so the caller can keep it for the weight gradient;  stage_flags [n * ceil(seg_rows / 128)] ints,
+//   zero before the first call; stage_epoch: a value that differs from every earlier call on the same flags.
+//   b_mn = 0: B is [N, K] (y = x W^T; epi 0 bias, 1 / 2 GELU erf / tanh with the pre-activation kept in aux);
+//   b_mn = 1: B is [K, N] (dgrad of a row-parallel linear; epi 0 only).
+extern "C" int tt_gemm_ag_bf16(void* const* a_ptrs, int n, int my_rank, int seg_rows, const void* b, int b_mn, long ldb,
+                               void* c, long ldc, const void* bias, void* aux, int N, int K, int epi, void* stage,
+                               int* stage_flags, int stage_epoch, int* status, void* stream) {
+    if (n < 2 || n > TT_MAX_PEERS || my_rank < 0 || my_rank >= n || seg_rows <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7))
+        return TT_ERR_ARG;
+    if (status == nullptr || stage == nullptr || stage_flags == nullptr || c == nullptr || (ldc & 7)) return TT_ERR_ARG;
+    if (epi < 0 || epi > 2 || (epi != 0 && (aux == nullptr || b_mn))) return TT_ERR_ARG;
+    const long M = (long)seg_rows * n;
+    if (M > 0x7fffffffL) return TT_ERR_ARG;
+    const int sms = sm_count();
+    const int BN = pick_bn((int)M, N, sms, false);
+    TmapArray tmA;
+    CUtensorMap tmB;
+    int rc;
+    for (int r = 0; r < n; ++r)
+        if ((rc = tt_make_tmap_2d(&tmA.m[r], a_ptrs[r], (uint64_t)seg_rows, (uint64_t)K, (uint64_t)K, BM, BK)) != TT_OK) return rc;
+    if ((rc = tt_make_tmap_2d(&tmA.m[TT_MAX_PEERS], stage, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK)) != TT_OK) return rc;
+    if (!b_mn) rc = tt_make_tmap_2d(&tmB, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, BK);
+    else rc = tt_make_tmap_2d(&tmB, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
+    if (rc != TT_OK) return rc;
+    GemmParams p;
+    default_params(p);
+    p.M = (int)M; p.N = N; p.K = K;
+    p.C = (__nv_bfloat16*)c;
+    p.ldc = ldc;
+    p.bias = (const __nv_bfloat16*)bias;
+    p.aux = (__nv_bfloat16*)aux;
+    p.status = status;
+    p.a_mode = 2;
+    p.a_nsrc = n;
+    p.n_dest = n;
+    p.n_seg = n;
+    p.seg_rows = seg_rows;
+    p.seg_rot = my_rank;                       // own rows first: they need no peer traffic
+    p.my_rank = my_rank;
+    p.tiles_m = n * ((seg_rows + BM - 1) / BM);
+    p.tiles_n = (N + BN - 1) / BN;
+    p.stage = (__nv_bfloat16*)stage;
+    p.stage_flags = stage_flags;
+    p.stage_epoch = stage_epoch;
+    for (int r = 0; r < n; ++r) p.peer_a[r] = (const __nv_bfloat16*)a_ptrs[r];
+    cudaStream_t st = (cudaStream_t)stream;
+    if (b_mn) return BN == 128 ? launch<128, false, true, 0, true>(tmA, tmB, p, sms, st)
+                               : launch<256, false, true, 0, true>(tmA, tmB, p, sms, st);
+    if (epi == 1) return BN == 128 ? launch<128, false, false, 1, true>(tmA, tmB, p, sms, st)
+                                   : launch<256, false, false, 1, true>(tmA, tmB, p, sms, st);
+    if (epi == 2) return BN == 128 ? launch<128, false, false, 2, true>(tmA, tmB, p, sms, st)
+                                   : launch<256, false, false, 2, true>(tmA, tmB, p, sms, st);
+    return BN == 128 ? launch<128, false, false, 0, true>(tmA, tmB, p, sms, st)
+                     : launch<256, false, false, 0, true>(tmA, tmB, p, sms, st);
+}
+
 // QKV projection with everything after it fused into the epilogue: bias, QK-RMSNorm, RoPE, and the Ulysses
 // sequence -> head all-to-all (each 128-column tile is one head's q, k or v and is stored straight into the
 // [batch, heads_per_rank, s_out, 128] buffer of the rank that owns the head, at token offset out_off).

@@ -181,6 +181,12 @@ class ParallelMLP(nn.Module):
         self.linear_fc2 = RowParallelLinear(hidden, dim, **kw)
 
     def forward(self, x):
+        if _use_fused_tp(x, self.linear_fc1.sequence_parallel, self.activation):
+            # token-sharded input: all-gather -> GEMM (+ activation), then GEMM -> reduce-scatter, both in-kernel over NVLink
+            from ...ops import fused_comm as FC
+            ws = _tp_workspace(x.shape[1], self.linear_fc1.in_features, self.linear_fc2.out_features)
+            h = FC.sp_column_linear(ws, x[0], self.linear_fc1.weight, self.linear_fc1.bias, self.activation)
+            return FC.sp_row_linear(ws, h, self.linear_fc2.weight, self.linear_fc2.bias)[None]
         return self.linear_fc2(self.linear_fc1(x, activation=self.activation))
 
 
@@ -248,6 +254,25 @@ def fused_comm_enabled() -> bool:
 def _use_fused(x: torch.Tensor, head_dim: int) -> bool:
     return (_FUSED_COMM and ps.get_context_parallel_world_size() > 1 and x.is_cuda and x.dtype == torch.bfloat16
             and x.shape[0] == 1 and head_dim == 128 and ops.get_impl() != "torch")
+
+
+_FUSED_TP_MIN_ROWS = 1024      # below this (the text stream) two device barriers cost more than the NCCL collectives
+
+
+def _use_fused_tp(x: torch.Tensor, sequence_parallel: bool, activation) -> bool:
+    """Sequence-parallel MLP through the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels."""
+    return (_FUSED_COMM and sequence_parallel and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3
+            and x.shape[0] == 1 and x.shape[1] >= _FUSED_TP_MIN_ROWS and ops.get_impl() != "torch"
+            and activation in (None, "gelu", "gelu_tanh"))
+
+
+def _tp_workspace(rows: int, k_max: int, n_max: int):
+    from ...ops.fused_comm import TPWorkspace
+    key = ("tp", rows, k_max, n_max)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = _WORKSPACES[key] = TPWorkspace(ps.get_tensor_model_parallel_group(), rows, max(k_max, n_max), max(k_max, n_max))
+    return ws
 
 
 def _workspace(heads_local: int, s: int, T: int):

@@ -14,7 +14,8 @@ from typing import Optional
 import torch
 
 _HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_HERE, "lib", "libteletron_b200.so")
+# TELETRON_B200_LIB points at an alternative build of the library (e.g. one compiled with other flags)
+LIB_PATH = os.environ.get("TELETRON_B200_LIB") or os.path.join(_HERE, "lib", "libteletron_b200.so")
 
 _lib: Optional[ctypes.CDLL] = None
 _err: str = ""

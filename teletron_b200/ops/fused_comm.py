@@ -419,6 +419,118 @@ def fused_linear_reduce_scatter(ws: TPWorkspace, x: torch.Tensor, w: torch.Tenso
     return out
 
 
+# ---- sequence-parallel linears with autograd (the model's MLPs under --sequence-parallel --fused-comm) ----------
+
+_GELU_KIND = {"gelu": 0, "gelu_tanh": 1}
+
+
+def _ag_gemm(ws: TPWorkspace, x_local: torch.Tensor, w: torch.Tensor, bias, b_mn: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``gather(x_local) @ op(w) (+ bias)`` and the gathered operand itself (kept by callers for the weight gradient).
+    ``b_mn = 0``: ``w`` is ``[N, K]``; ``b_mn = 1``: ``w`` is ``[K, N]``."""
+    rows, K = x_local.shape
+    if rows != ws.rows or K > ws.k_max:
+        raise _lib.NativeError("operand does not match the workspace")
+    src = ws.heap.tensor(ws.off_a, (rows, K), BF16)
+    ws.heap.barrier()                       # every rank has finished reading the previous gather source
+    src.copy_(x_local)
+    ws.heap.barrier()
+    N = w.shape[1] if b_mn else w.shape[0]
+    M = rows * ws.tp
+    out = torch.empty(M, N, dtype=BF16, device=w.device)
+    xg = torch.empty(M, K, dtype=BF16, device=w.device)
+    ws.epoch += 1
+    call("tt_gemm_ag_bf16", ws.heap.ptr_table(ws.off_a), c_int(ws.tp), c_int(ws.rank), c_int(rows), ptr(w), c_int(b_mn),
+         c_long(w.stride(0)), ptr(out), c_long(N), ptr(bias), None, c_int(N), c_int(K), c_int(0), ptr(xg), ptr(ws.flags),
+         c_int(ws.epoch), ptr(status_tensor(w.device)), stream())
+    # the kernel stages only the remote row blocks; this rank's own block completes the gathered operand
+    xg[ws.rank * rows:(ws.rank + 1) * rows].copy_(x_local)
+    return out, xg
+
+
+def _gemm_rs(ws: TPWorkspace, x: torch.Tensor, w: torch.Tensor, b_mn: int, bias=None) -> torch.Tensor:
+    """``reduce_scatter(x @ op(w)) (+ bias)`` over row blocks: partial tiles are pushed to the block's owner from the
+    GEMM epilogue, then the owner sums the ``tp`` partials."""
+    M, K = x.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    if M != ws.rows * ws.tp or N > ws.n_max:
+        raise _lib.NativeError("operand does not match the workspace")
+    ws.heap.barrier()                       # previous partials have been consumed everywhere
+    call("tt_gemm_comm_bf16", _table([x.data_ptr()]), c_int(ws.tp), c_int(0), c_long(M), c_int(0), c_int(0), None, c_long(0),
+         ptr(w), c_int(b_mn), c_long(w.stride(0)), None, c_long(0), None, c_int(M), c_int(N), c_int(K), c_int(ws.rows),
+         c_int(ws.rank), c_int(2), ws.heap.ptr_table(ws.off_s), c_int(0), c_int(0), c_long(N), None, None, c_int(0),
+         ptr(status_tensor(x.device)), stream())
+    ws.heap.barrier()                       # all partials have landed
+    out = torch.empty(ws.rows, N, dtype=BF16, device=x.device)
+    stage = ws.heap.tensor(ws.off_s, (ws.tp, ws.rows, N), BF16)
+    call("tt_partial_sum", ptr(stage), c_int(ws.tp), c_long(ws.rows), c_int(N), ptr(bias), None, None, c_long(ws.rows),
+         ptr(out), stream())
+    return out
+
+
+class _SPColumnLinear(torch.autograd.Function):
+    """Column-parallel linear on a token-sharded input: all-gather -> GEMM forward; the data gradient is a
+    GEMM -> reduce-scatter, the weight gradient uses the gathered operand kept from the forward."""
+
+    @staticmethod
+    def forward(ctx, ws, x, w, bias, activation):
+        u, xg = _ag_gemm(ws, check(x.contiguous(), BF16, "x"), w, bias, 0)
+        ctx.ws, ctx.activation, ctx.has_bias = ws, activation, bias is not None
+        if activation is None:
+            ctx.save_for_backward(xg, w)
+            return u
+        y = torch.empty_like(u)
+        call("tt_gelu_fwd", ptr(u), ptr(y), c_long(u.numel()), c_int(_GELU_KIND[activation]), stream())
+        ctx.save_for_backward(xg, w, u)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy = check(dy.contiguous(), BF16, "dy")
+        if ctx.activation is None:
+            xg, w = ctx.saved_tensors
+            du = dy
+        else:
+            xg, w, u = ctx.saved_tensors
+            du = torch.empty_like(u)
+            call("tt_gelu_bwd", ptr(dy), ptr(u), ptr(du), c_long(u.numel()), c_int(_GELU_KIND[ctx.activation]), stream())
+        dx = _gemm_rs(ctx.ws, du, w, 1) if ctx.needs_input_grad[1] else None
+        dw = gemm.gemm_tn(du, xg) if ctx.needs_input_grad[2] else None
+        db = du.sum(dim=0, dtype=torch.float32).to(BF16) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        return None, dx, dw, db, None
+
+
+class _SPRowLinear(torch.autograd.Function):
+    """Row-parallel linear producing a token-sharded output: GEMM -> reduce-scatter forward (bias added once, by the
+    owner of each row block); the data gradient is an all-gather -> GEMM and its gathered operand feeds the weight
+    gradient.  The bias gradient is this rank's row block's share (summed over TP with the other partial gradients)."""
+
+    @staticmethod
+    def forward(ctx, ws, x, w, bias):
+        x = check(x.contiguous(), BF16, "x")
+        ctx.ws, ctx.has_bias = ws, bias is not None
+        ctx.save_for_backward(x, w)
+        return _gemm_rs(ws, x, w, 0, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = check(dy.contiguous(), BF16, "dy")
+        dx, dyg = _ag_gemm(ctx.ws, dy, w, None, 1)
+        dw = gemm.gemm_tn(dyg, x) if ctx.needs_input_grad[2] else None
+        db = dy.sum(dim=0, dtype=torch.float32).to(BF16) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        return None, dx, dw, db
+
+
+def sp_column_linear(ws: TPWorkspace, x: torch.Tensor, w: torch.Tensor, bias=None, activation: Optional[str] = None) -> torch.Tensor:
+    """``act(all_gather(x) @ w^T + bias)`` for ``x [rows, K]`` token-sharded over the tensor-parallel group."""
+    return _SPColumnLinear.apply(ws, x, w, bias, activation)
+
+
+def sp_row_linear(ws: TPWorkspace, x: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tensor:
+    """``reduce_scatter(x @ w^T) + bias`` for ``x [tp * rows, K / tp]``; returns this rank's ``[rows, N]`` block."""
+    return _SPRowLinear.apply(ws, x, w, bias)
+
+
 # ---------------------------------------------------------------------------------------------
 # F4: data-parallel gradient reduce-scatter (+ scale) and parameter all-gather over peer memory
 # ---------------------------------------------------------------------------------------------

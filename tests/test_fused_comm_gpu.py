@@ -107,6 +107,40 @@ def test_tp_all_gather_gemm_and_gemm_reduce_scatter():
     """)
 
 
+def test_sequence_parallel_mlp_fused_matches_nccl_path():
+    """The model's MLP under sequence parallelism: fused all-gather -> GEMM / GEMM -> reduce-scatter (forward and
+    backward) against the NCCL all-gather / reduce-scatter composition; 1100 rows per rank (not a tile multiple)."""
+    _run_ranks("""
+        from teletron_b200.parallel import state as ps
+        from teletron_b200.models.hunyuanvideo import blocks as B
+        ps.initialize_model_parallel(world, 1)
+        torch.manual_seed(3)
+        rows, dim, hidden = 1100, 512, 1536
+        mlp = B.ParallelMLP(dim, hidden, "gelu_tanh", tp=world, sequence_parallel=True, device="cuda", dtype=torch.bfloat16)
+        g = torch.Generator(device="cuda").manual_seed(11 + rank)
+        with torch.no_grad():
+            for p_ in mlp.parameters():
+                p_.copy_((torch.randn(p_.shape, device="cuda", generator=g) * 0.05).to(p_.dtype))
+        x = torch.randn(1, rows, dim, device="cuda", generator=g).bfloat16()
+        dy = torch.randn(1, rows, dim, device="cuda", generator=g).bfloat16()
+        res = {}
+        for fused in (False, True, True):
+            B.set_fused_comm(fused)
+            xi = x.clone().requires_grad_(True)
+            for p_ in mlp.parameters():
+                p_.grad = None
+            y = mlp(xi)
+            y.backward(dy)
+            res[fused] = [y.detach(), xi.grad] + [p_.grad.clone() for p_ in mlp.parameters()]
+        names = ["y", "dx"] + [n for n, _ in mlp.named_parameters()]
+        for n, a, b in zip(names, res[True], res[False]):
+            assert torch.isfinite(a.float()).all(), n
+            assert rel(a, b) < 1.5e-2, (n, rel(a, b))
+        for ws in B._WORKSPACES.values():
+            ws.heap.check()
+    """)
+
+
 def test_grad_reduce_scatter_and_param_all_gather():
     _run_ranks("""
         from teletron_b200.ops import fused_comm as FC
