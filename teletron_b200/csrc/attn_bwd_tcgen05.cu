@@ -8,23 +8,25 @@
 //     (K, V).   T1 = Q K^T = S,  T2 = dO V^T = dP,  dS = exp2(S * c - lse[row]) * (dP - delta[row]),
 //     dQ += dS K.
 //
-// Both run the same pipeline.  Stationary operands [128 x 128] are loaded once; streamed chunks are 128 rows
-// ([128 x 128] x 2 operands per stage, two TMA stages).  Chunks of 128 keep every MMA at N = 128: an N = 64
-// instruction was measured to take as long as an N = 128 one on this part, so 64-row chunks ran the T products at
-// half rate.  T1 and T2 are single-buffered in tensor memory and the overlap comes from the order of issue:
+// Both run the same pipeline.  Stationary operands [128 x 128] are loaded once; streamed chunks are 128 rows,
+// held in two TMA rings (three slots for the operand that the score product needs early and dK / dQ needs last,
+// two for the other).  Chunks of 128 keep every MMA at N = 128: an N = 64 instruction was measured to take as long
+// as an N = 128 one on this part.  T1 and T2 are single-buffered in tensor memory; the overlap comes from keeping P
+// in registers between the two softmax passes, so that T1 is free for the next chunk's scores while dS is formed:
 //
-//   tensor core:  ... dV(c) | S(c+1) | dK(c) | dP(c+1) | dV(c+1) | S(c+2) ...
-//   softmax:      ... dS(c) ........ | P(c+1) .......... | dS(c+1) ........ ...
+//   tensor core:  S(c+1) ......... | dK(c) dV(c) dP(c+1) | S(c+2) ........ | dK(c+1) ...
+//   softmax:      dS(c) .......... | P(c+1) ............ | dS(c+1) ....... | P(c+2) ...
 //
-// S(c+1) may overwrite T1 as soon as dV(c) has consumed P(c); dP(c+1) may overwrite T2 as soon as dK(c) has
-// consumed dS(c); the tensor core executes in issue order, so these hazards need no extra barrier.  The eight softmax
-// warps (one stationary row x 64 streamed columns per thread) write bf16 P / dS back over T1 / T2, consumed from
-// tensor memory as the A operand of the accumulator MMAs; P stays packed in registers between the two passes.  The
-// streamed chunk is used twice from the same shared-memory bytes: as a K-major B operand for the T products and as
-// an MN-major B operand for the accumulator updates.
+// The sixteen softmax warps (one stationary row x 32 streamed columns per thread) read S from T1 and keep bf16 P in
+// registers (the special-function unit's 16 exp2 per clock make this pass ~1250 clocks per chunk), then read dP from
+// T2 and write bf16 P and dS back over the dP columns they have just read; both are consumed from tensor memory as
+// the A operand of the accumulator MMAs.  dP(c+1) may overwrite T2 as soon as dK(c) / dV(c) have consumed it; the
+// tensor core executes in issue order, so that hazard needs no extra barrier.  A streamed chunk is used twice from
+// the same shared-memory bytes: as a K-major B operand for the T products and as an MN-major B operand for the
+// accumulator updates.
 //
-//   TMEM columns: [0,128) T1 = S (P aliases [0,32) and [64,96)), [128,256) T2 = dP (dS aliases [128,160) and
-//                 [192,224)), [256,384) accumulator 1, [384,512) accumulator 2.
+//   TMEM columns: [0,128) T1 = S, [128,256) T2 = dP (of every 32 columns, P aliases the first 16 and dS the last 16),
+//                 [256,384) accumulator 1, [384,512) accumulator 2.
 //
 // q, k, v, dq, dk, dv: [B*H, S, 128] bf16 head-major; dout: [B, S, H*128] bf16 token-major;
 // lse, delta: [B*H, pitch] fp32 (delta = rowsum(dO * O), computed by the preprocess kernel below).
@@ -40,12 +42,14 @@ using namespace sm100;
 constexpr int D = 128;
 constexpr int BS = 128;            // stationary rows
 constexpr int BC = 128;            // streamed rows per chunk
-constexpr int kStages = 2;
-constexpr int kThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2-9 softmax / epilogue (two warpgroups)
+constexpr int kRing1 = 3;           // slots of the first streamed operand (Q or K): used by the score product and, last, by dK / dQ
+constexpr int kRing2 = 2;           // slots of the second streamed operand (dO or V)
+constexpr int kGroups = 4;         // softmax warpgroups: each owns 128 / kGroups streamed columns of every chunk
+constexpr int kCols = BC / kGroups; // 32: one tcgen05.ld per pass and thread
+constexpr int kThreads = 64 + 128 * kGroups;   // warp 0 TMA, warp 1 MMA, then the softmax / epilogue warpgroups
 constexpr int kSlab = 128 * 128;           // [128 rows x 64 columns] bf16 slab, 128-byte rows: 16 KB
 constexpr int kTile = 2 * kSlab;           // [128 x 128]: 32 KB
-constexpr int kStageBytes = 2 * kTile;     // two streamed operands per stage: 64 KB
-constexpr int kSmemBytes = 2 * kTile + kStages * kStageBytes + 1024 /* stats */ + 256 /* barriers */ + 1024;
+constexpr int kSmemBytes = (2 + kRing1 + kRing2) * kTile + 256 /* barriers */ + 1024 /* alignment */;   // 225.3 KB
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -91,15 +95,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sA1 = base;                       // stationary operand 1 (K or Q)
     const uint32_t sA2 = base + kTile;               // stationary operand 2 (V or dO)
-    const uint32_t sRing = base + 2 * kTile;         // stage: [B1 chunk (Q or K) | B2 chunk (dO or V)]
-    const uint32_t bars = base + 2 * kTile + kStages * kStageBytes + 1024;
+    const uint32_t sRing1 = base + 2 * kTile;                        // slots of streamed operand 1 (Q or K)
+    const uint32_t sRing2 = sRing1 + kRing1 * kTile;                 // slots of streamed operand 2 (dO or V)
+    const uint32_t bars = sRing2 + kRing2 * kTile;
     const uint32_t a_full = bars;
-    auto b_full = [&](int s) { return bars + 8u * (1 + s); };
-    auto b_empty = [&](int s) { return bars + 8u * (1 + kStages + s); };
-    const uint32_t s_full = bars + 8u * (1 + 2 * kStages);     // T1 = S holds this chunk's scores
+    auto b1_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto b1_empty = [&](int s) { return bars + 8u * (1 + kRing1 + s); };
+    auto b2_full = [&](int s) { return bars + 8u * (1 + 2 * kRing1 + s); };
+    auto b2_empty = [&](int s) { return bars + 8u * (1 + 2 * kRing1 + kRing2 + s); };
+    const uint32_t s_full = bars + 8u * (1 + 2 * kRing1 + 2 * kRing2);   // T1 = S holds this chunk's scores
     const uint32_t dp_full = s_full + 8u;                      // T2 = dP holds this chunk's products
-    const uint32_t p_ready = s_full + 16u;                     // S has been read (and P written back, KV-stationary)
-    const uint32_t ds_ready = s_full + 24u;                    // dS has been written over dP
+    const uint32_t p_ready = s_full + 16u;                     // every softmax warp has read S (P is in registers)
+    const uint32_t ds_ready = s_full + 24u;                    // P and dS have been written over dP
     const uint32_t acc_final = s_full + 32u;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,14 +119,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (threadIdx.x == 0) {
         abort_flag = 0;
         mbar_init(a_full, 1);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(b_full(s), 1);
-            mbar_init(b_empty(s), 1);
+        for (int s = 0; s < kRing1; ++s) {
+            mbar_init(b1_full(s), 1);
+            mbar_init(b1_empty(s), 1);
+        }
+        for (int s = 0; s < kRing2; ++s) {
+            mbar_init(b2_full(s), 1);
+            mbar_init(b2_empty(s), 1);
         }
         mbar_init(s_full, 1);
         mbar_init(dp_full, 1);
-        mbar_init(p_ready, 8);
-        mbar_init(ds_ready, 8);
+        mbar_init(p_ready, 4 * kGroups);
+        mbar_init(ds_ready, 4 * kGroups);
         mbar_init(acc_final, 1);
         fence_barrier_init();
         fence_proxy_async();
@@ -149,20 +160,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 }
             }
             for (int c = 0; c < n_chunks; ++c) {
-                const int s = c % kStages;
-                const uint32_t ph = (uint32_t)(c / kStages) & 1u;
-                if (!mbar_wait(b_empty(s), ph ^ 1u, &abort_flag)) goto done;
-                mbar_arrive_expect_tx(b_full(s), kStageBytes);
-                const uint32_t dst = sRing + s * kStageBytes;
+                const int s1 = c % kRing1, s2 = c % kRing2;
+                if (!mbar_wait(b1_empty(s1), ((uint32_t)(c / kRing1) & 1u) ^ 1u, &abort_flag)) goto done;
+                mbar_arrive_expect_tx(b1_full(s1), kTile);
+                const uint32_t d1 = sRing1 + s1 * kTile;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (KVS) {
-                        tma_load_3d(dst + h * kSlab, &tmQ, b_full(s), h * 64, c * BC, bh);
-                        tma_load_4d(dst + kTile + h * kSlab, &tmDO, b_full(s), h * 64, head, c * BC, b);
-                    } else {
-                        tma_load_3d(dst + h * kSlab, &tmK, b_full(s), h * 64, c * BC, bh);
-                        tma_load_3d(dst + kTile + h * kSlab, &tmV, b_full(s), h * 64, c * BC, bh);
-                    }
+                    if (KVS) tma_load_3d(d1 + h * kSlab, &tmQ, b1_full(s1), h * 64, c * BC, bh);
+                    else tma_load_3d(d1 + h * kSlab, &tmK, b1_full(s1), h * 64, c * BC, bh);
+                }
+                if (!mbar_wait(b2_empty(s2), ((uint32_t)(c / kRing2) & 1u) ^ 1u, &abort_flag)) goto done;
+                mbar_arrive_expect_tx(b2_full(s2), kTile);
+                const uint32_t d2 = sRing2 + s2 * kTile;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (KVS) tma_load_4d(d2 + h * kSlab, &tmDO, b2_full(s2), h * 64, head, c * BC, b);
+                    else tma_load_3d(d2 + h * kSlab, &tmV, b2_full(s2), h * 64, c * BC, bh);
                 }
             }
         }
@@ -184,36 +197,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t sb, bool first) {
 #pragma unroll
                 for (int kk = 0; kk < BC / 16; ++kk)
-                    umma_bf16_ts(tmem + acc_col, tmem + a_col + (kk >> 2) * 64 + (kk & 3) * 8,
+                    umma_bf16_ts(tmem + acc_col, tmem + a_col + (kk >> 1) * kCols + (kk & 1) * 8,
                                  smem_desc_sw128(sb + kk * 2048, kSlab, 1024), idesc_a, (first && kk == 0) ? 0u : 1u);
             };
             if (!mbar_wait(a_full, 0, &abort_flag)) goto done;
-            if (!mbar_wait(b_full(0), 0, &abort_flag)) goto done;
+            if (!mbar_wait(b1_full(0), 0, &abort_flag)) goto done;
             tc_fence_after();
-            issue_t(kT1, sA1, sRing);
+            issue_t(kT1, sA1, sRing1);
             umma_commit(s_full);
-            issue_t(kT2, sA2, sRing + kTile);
+            if (!mbar_wait(b2_full(0), 0, &abort_flag)) goto done;
+            tc_fence_after();
+            issue_t(kT2, sA2, sRing2);
             umma_commit(dp_full);
             for (int c = 0; c < n_chunks; ++c) {
                 const uint32_t par = (uint32_t)c & 1u;
-                const uint32_t sb = sRing + (c % kStages) * kStageBytes;
                 const bool more = c + 1 < n_chunks;
-                const uint32_t sb_next = sRing + ((c + 1) % kStages) * kStageBytes;
+                // T1 is free as soon as every softmax warp has read S(c): the next chunk's scores overlap the dS pass
                 if (!mbar_wait(p_ready, par, &abort_flag)) goto done;
                 tc_fence_after();
-                if (KVS) issue_acc(kAcc1, kT1, sb + kTile, c == 0);          // dV += P^T dO
                 if (more) {
-                    if (!mbar_wait(b_full((c + 1) % kStages), (uint32_t)((c + 1) / kStages) & 1u, &abort_flag)) goto done;
+                    const int n1 = (c + 1) % kRing1;
+                    if (!mbar_wait(b1_full(n1), (uint32_t)((c + 1) / kRing1) & 1u, &abort_flag)) goto done;
                     tc_fence_after();
-                    issue_t(kT1, sA1, sb_next);                              // next chunk's scores: overlaps the dS pass
+                    issue_t(kT1, sA1, sRing1 + n1 * kTile);
                     umma_commit(s_full);
                 }
+                // T2 now holds bf16 P (first 16 columns of every 32) and dS (last 16) of this chunk
                 if (!mbar_wait(ds_ready, par, &abort_flag)) goto done;
                 tc_fence_after();
-                issue_acc(KVS ? kAcc2 : kAcc1, kT2, sb, c == 0);             // dK += dS^T Q   /   dQ += dS K
-                umma_commit(b_empty(c % kStages));
+                issue_acc(KVS ? kAcc2 : kAcc1, kT2 + 16, sRing1 + (c % kRing1) * kTile, c == 0);   // dK += dS^T Q  /  dQ += dS K
+                umma_commit(b1_empty(c % kRing1));
+                if (KVS) issue_acc(kAcc1, kT2, sRing2 + (c % kRing2) * kTile, c == 0);             // dV += P^T dO
+                umma_commit(b2_empty(c % kRing2));
                 if (more) {
-                    issue_t(kT2, sA2, sb_next + kTile);                      // next chunk's dP: overlaps its P pass
+                    const int n2 = (c + 1) % kRing2;
+                    if (!mbar_wait(b2_full(n2), (uint32_t)((c + 1) / kRing2) & 1u, &abort_flag)) goto done;
+                    tc_fence_after();
+                    issue_t(kT2, sA2, sRing2 + n2 * kTile);                                        // next chunk's dP
                     umma_commit(dp_full);
                 }
             }
@@ -221,11 +241,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------ softmax / dS
-        // Two warpgroups share every chunk: a thread owns one stationary row and 64 of the chunk's 128 streamed
-        // rows (columns of T1 / T2; warpgroup 0: [0, 64), warpgroup 1: [64, 128)).  Each chunk has two passes:
+        // The warpgroups share every chunk: a thread owns one stationary row and kCols = 32 of the chunk's 128
+        // streamed rows (columns of T1 / T2; warpgroup g: [32 g, 32 g + 32)), so four warps per scheduler hide each
+        // other's tcgen05.ld / exp2 / tcgen05.st latency.  Each chunk has two passes:
         // P from the scores (runs while the tensor core forms dP), then dS from dP (runs while it forms the
         // next chunk's scores and, KV-stationary, dV).
-        const int half = (warp - 2) >> 2;
+        const int part = (warp - 2) >> 2;
         const int quad = warp & 3;
         const int srow = quad * 32 + lane;                 // row within the stationary tile
         const int row = r0 + srow;                         // key (KVS) or query index
@@ -240,23 +261,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             my_lse = row_live ? p.lse[(long)bh * p.pitch + row] * kLog2e : INFINITY;
             my_delta = row_live ? p.delta[(long)bh * p.pitch + row] : 0.f;
         }
-        const uint32_t t1 = tmem + lane_sel + kT1 + half * 64, t2 = tmem + lane_sel + kT2 + half * 64;
+        const uint32_t t1 = tmem + lane_sel + kT1 + part * kCols, t2 = tmem + lane_sel + kT2 + part * kCols;
         for (int c = 0; c < n_chunks; ++c) {
             const uint32_t par = (uint32_t)c & 1u;
-            const int col0 = c * BC + half * 64;           // first streamed row of this thread's 64 columns
+            const int col0 = c * BC + part * kCols;         // first streamed row of this thread's 32 columns
             // KV-stationary: the streamed queries each have their own lse / delta; every thread reads them straight
             // from global memory (same addresses across the warp, so each load is one broadcast).  The statistics
-            // rows are `pitch` long (a multiple of 64): a 64-column group past the end has no live query.
+            // rows are `pitch` long (a multiple of 64): a 32-column group past the end has no live query.
             const bool cols_ok = !KVS || col0 < p.pitch;
             const float4* lse4 = reinterpret_cast<const float4*>(p.lse + (long)bh * p.pitch + col0);
             const float4* del4 = reinterpret_cast<const float4*>(p.delta + (long)bh * p.pitch + col0);
-            uint32_t pk[32];
+            uint32_t pk[16];
             if (!mbar_wait(s_full, par, &abort_flag)) goto done;
             tc_fence_after();
-#pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
+            {
+                constexpr int pass = 0;
                 uint32_t a[32];
-                tmem_ld_32x32(t1 + pass * 32, a);
+                tmem_ld_32x32(t1, a);
                 float4 lq[8];
                 if (KVS) {
 #pragma unroll
@@ -287,23 +308,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     pk[pass * 16 + i] = *reinterpret_cast<const uint32_t*>(&pb);
                 }
             }
-            if (KVS) {
-                // bf16 pairs over the first 32 of the 64 columns this thread has just read
-                tmem_st_32x16(t1, pk);
-                tmem_st_32x16(t1 + 16, pk + 16);
-                tmem_st_wait();
-            }
+            // P stays in registers: T1 is released to the next chunk's score product right away
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
 
             if (!mbar_wait(dp_full, par, &abort_flag)) goto done;
             tc_fence_after();
-            uint32_t dk[32];
-#pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
+            uint32_t dk[16];
+            {
+                constexpr int pass = 0;
                 uint32_t g[32];
-                tmem_ld_32x32(t2 + pass * 32, g);
+                tmem_ld_32x32(t2, g);
                 float4 dq4[8];
                 if (KVS) {
 #pragma unroll
@@ -327,8 +343,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     dk[pass * 16 + i] = *reinterpret_cast<const uint32_t*>(&db);
                 }
             }
-            tmem_st_32x16(t2, dk);
-            tmem_st_32x16(t2 + 16, dk + 16);
+            // bf16 pairs over the 32 dP columns this thread has just read: P in the first 16, dS in the last 16
+            if (KVS) tmem_st_32x16(t2, pk);
+            tmem_st_32x16(t2 + 16, dk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -346,7 +363,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float mul = (KVS && which == 0) ? 1.f : p.scale;
             const uint32_t tacc = tmem + lane_sel + kAcc1 + which * 128;
 #pragma unroll 1
-            for (int cch = half * 2; cch < half * 2 + 2; ++cch) {      // each warpgroup stores half of the columns
+            for (int cch = part; cch < D / 32; cch += kGroups) {        // the warpgroups share the accumulator's columns
                 uint32_t r[32];
                 tmem_ld_32x32(tacc + cch * 32, r);
                 tmem_ld_wait();
