@@ -50,6 +50,8 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-save-attention", action="store_true")
     p.add_argument("--fused-comm", type=int, default=1, help="1: in-kernel NVLink collectives for context parallelism")
+    p.add_argument("--sequence-parallel", type=int, default=0,
+                   help="1: shard the residual stream's tokens over the tensor-parallel ranks (all-gather -> GEMM / GEMM -> reduce-scatter)")
     return p.parse_args()
 
 
@@ -158,6 +160,9 @@ def main():
         argv += ["--recompute-granularity", "full", "--recompute-method", "block"]
     if a.impl == "ours" and a.fused_comm and a.gpus > 1:
         argv += ["--fused-comm"]
+    sp = bool(a.sequence_parallel) and tp > 1
+    if sp:
+        argv += ["--sequence-parallel"]
     args = initialize(argv=argv)
     dev = args.device
     rank = args.rank
@@ -166,8 +171,8 @@ def main():
     cfg = hunyuan_13b(in_channels=33 if a.model_type == "i2v" else 16, num_layers=a.layers,
                       num_single_layers=a.single_layers,
                       recompute_granularity=None if a.no_recompute else "full", seed=1234,
-                      recompute_save_attention=not a.no_save_attention and a.impl == "ours")
-    if a.impl == "ours" and a.fused_comm and cp > 1:
+                      recompute_save_attention=not a.no_save_attention and a.impl == "ours", sequence_parallel=sp)
+    if a.impl == "ours" and a.fused_comm and a.gpus > 1:
         from teletron_b200.models.hunyuanvideo import blocks
         blocks.set_fused_comm(True)
     flow = FlowConfig(shift=7.0, model_type=a.model_type)
@@ -256,9 +261,9 @@ def main():
                "data": "synthetic latents/embeddings, random-init weights", "impl": a.impl,
                "config": {"model": f"HunyuanVideo-13B {a.model_type.upper()} ({a.layers} dual + {a.single_layers} single blocks, hidden 3072)",
                           "global_batch": 1, "seq_len": tokens + a.text_len, "frames": a.frames,
-                          "resolution": f"{W}x{H}", "parallelism": f"tp{tp}cp{cp}dp1",
+                          "resolution": f"{W}x{H}", "parallelism": f"tp{tp}cp{cp}dp1" + ("+sp" if sp else ""),
                           "recompute": "none" if a.no_recompute else ("full (attention output kept)" if cfg.recompute_save_attention else "full"),
-                          "collectives": "in-kernel NVLink (fused)" if (a.impl == "ours" and a.fused_comm and cp > 1) else "NCCL", "optimizer": "AdamW ZeRO-1",
+                          "collectives": "in-kernel NVLink (fused)" if (a.impl == "ours" and a.fused_comm and (cp > 1 or sp)) else "NCCL", "optimizer": "AdamW ZeRO-1",
                           "optimizer_state": "split16 master + bf16 moments" if single else "fp32 master + fp32 moments",
                           "l2": "inputs larger than L2: >25 GB of weights and >10 GB of activations stream through every step"},
                "s_per_step": ms_per_step / 1e3, "frames_per_s": value * a.frames,

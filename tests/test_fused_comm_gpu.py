@@ -211,3 +211,47 @@ def test_fused_ulysses_model_matches_nccl_path():
         from teletron_b200.ops.gemm_tcgen05 import check_status
         check_status()
     """, timeout=900)
+
+
+def test_sequence_parallel_model_fused_matches_plain_tensor_parallel():
+    """One dual + one single block at full width, tp = 2: token-sharded residual stream with the fused all-gather -> GEMM /
+    GEMM -> reduce-scatter MLPs against plain tensor parallelism (replicated activations, NCCL all-reduce)."""
+    _run_ranks("""
+        from teletron_b200.models.hunyuanvideo import FlowConfig, HunyuanPipeline, hunyuan_13b
+        from teletron_b200.models.hunyuanvideo import blocks
+        from teletron_b200.parallel import state as ps
+        from teletron_b200.parallel.grad_buffer import allreduce_tp_partial_grads
+        ps.initialize_model_parallel(2, 1)
+        gen = torch.Generator().manual_seed(0)
+        batch = {"latents": torch.randn(1, 16, 3, 60, 64, generator=gen), "prompt_embeds": torch.randn(1, 40, 4096, generator=gen),
+                 "clip_text_embed": torch.randn(1, 768, generator=gen)}       # 3*30*32 = 2880 video tokens: 1440 per rank
+        junk = [torch.full((64 << 20,), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(8)]
+        del junk
+        res = {}
+        for sp in (True, False):
+            blocks.set_fused_comm(sp)
+            cfg = hunyuan_13b(in_channels=16, num_layers=1, num_single_layers=1, recompute_granularity="full", sequence_parallel=sp)
+            pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"), device=torch.device("cuda", rank), dtype=torch.bfloat16)
+            for it in range(2):
+                for p_ in pipe.transformer.parameters():
+                    p_.grad = None
+                pipe.step = 0
+                loss = pipe(batch)[0]
+                loss.backward()
+            allreduce_tp_partial_grads(list(pipe.transformer.parameters()), ps.get_tensor_model_parallel_group())
+            res[sp] = (float(loss.detach()), {n: p_.grad.float().clone() for n, p_ in pipe.transformer.named_parameters() if p_.grad is not None})
+            assert all(torch.isfinite(g).all() for g in res[sp][1].values()), "non-finite gradient"
+        assert abs(res[True][0] - res[False][0]) < 2e-2 * abs(res[False][0]), (res[True][0], res[False][0])
+        bad = []
+        for n, gref in res[False][1].items():
+            if n.endswith("to_k.bias"):
+                continue
+            r = rel(res[True][1][n], gref)
+            if r > 0.08:
+                bad.append((n, r))
+        assert not bad, bad[:8]
+        from teletron_b200.ops.gemm_tcgen05 import check_status
+        check_status()
+        for ws in blocks._WORKSPACES.values():
+            ws.heap.check()
+    """, timeout=900)
