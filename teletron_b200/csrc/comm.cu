@@ -54,14 +54,23 @@ __global__ void barrier_kernel(PeerTable flags, int my_rank, int n, unsigned lon
 __global__ void __launch_bounds__(256) reduce_scatter_kernel(PeerTable src, int n, long offset, __nv_bfloat16* __restrict__ out,
                                                             long nvec, float scale) {
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+        // all peers' loads are issued before the first one is consumed: a peer load takes ~2 us to come back, so the
+        // number of loads in flight per thread sets the NVLink bandwidth this kernel reaches
+        bf16x8 t[TT_MAX_PEERS];
+#pragma unroll
+        for (int r = 0; r < TT_MAX_PEERS; ++r)
+            if (r < n) t[r] = ld8(reinterpret_cast<const __nv_bfloat16*>(src.ptr[r]) + offset + i * 8);
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int r = 0; r < n; ++r) {
-            float v[8];
-            unpack8(ld8(reinterpret_cast<const __nv_bfloat16*>(src.ptr[r]) + offset + i * 8), v);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        for (int r = 0; r < TT_MAX_PEERS; ++r) {
+            if (r < n) {
+                float v[8];
+                unpack8(t[r], v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += v[j];
+            }
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] *= scale;

@@ -281,7 +281,17 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
             const __nv_bfloat16* src = p.peer_a[seg] + (long)r0 * p.K;
             __nv_bfloat16* dst = p.stage + ((long)seg * p.seg_rows + r0) * p.K;
             const long nvec = (long)nrows * row_vecs;
-            for (long v = tid; v < nvec; v += 128) tt::st8(dst + v * 8, tt::ld8(src + v * 8));
+            // eight 16-byte peer loads in flight per thread: one outstanding load per thread leaves NVLink mostly idle
+            // (a load takes ~2 us to come back; 128 threads x 148 CTAs x 16 B per round trip is ~150 GB/s)
+            long v = tid;
+            for (; v + 7 * 128 < nvec; v += 8 * 128) {
+                tt::bf16x8 t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) t[u] = tt::ld8(src + (v + u * 128) * 8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) tt::st8(dst + (v + u * 128) * 8, t[u]);
+            }
+            for (; v < nvec; v += 128) tt::st8(dst + v * 8, tt::ld8(src + v * 8));
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");        // only the copier warps take part; no waits in this loop
             if (tid == 0) st_release(p.stage_flags + seg * tiles_per_seg + mt, p.stage_epoch);
@@ -301,8 +311,16 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
             const int row = seg * p.seg_rows + lrow;                // row of the logical output
             const bool row_ok = lrow < p.seg_rows && row < p.M;
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+            const uint32_t tacc_tile = tacc;
+            const int n0_tile = n0;
             if (EPI == 5) {
-                // ---- fused QKV epilogue: this 128-column tile is one head's q, k or v ----
+              // ---- fused QKV epilogue: every 128 columns of the tile are one head's q, k or v ----
+              // (256-wide tiles keep the tensor core at N = 256; the epilogue walks the two heads one after the other)
+#pragma unroll 1
+              for (int hh = 0; hh < BN / 128; ++hh) {
+                const int n0 = n0_tile + hh * 128;
+                if (n0 >= p.N) break;
+                const uint32_t tacc = tacc_tile + hh * 128;
                 const int idx = n0 / 128;
                 const int head = idx / 3, which = idx - head * 3;
                 const int dest = head / p.heads_per_rank, hl = head - dest * p.heads_per_rank;
@@ -362,6 +380,7 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
 #pragma unroll
                     for (int g = 0; g < 16; ++g) tt::st8(drow + g * 8, tt::pack8(v + g * 8));
                 }
+              }
             } else {
                 // where this tile's rows land: local C, the owner rank of a column block, or an owner's staging slot
                 __nv_bfloat16* crow;
@@ -453,7 +472,7 @@ int dispatch(bool a_mn, bool b_mn, int epi, const TmapArray& tmA, const CUtensor
         if (epi == 0) return launch<BN, false, false, 0>(tmA, tmB, p, sms, st);
         if (epi == 1) return launch<BN, false, false, 1>(tmA, tmB, p, sms, st);
         if (epi == 2) return launch<BN, false, false, 2>(tmA, tmB, p, sms, st);
-        if (epi == 5 && BN == 128) return launch<128, false, false, 5>(tmA, tmB, p, sms, st);
+        if (epi == 5) return launch<BN, false, false, 5>(tmA, tmB, p, sms, st);
     } else if (!a_mn && b_mn) {
         if (epi == 0) return launch<BN, false, true, 0>(tmA, tmB, p, sms, st);
         if (epi == 3) return launch<BN, false, true, 3>(tmA, tmB, p, sms, st);
@@ -765,7 +784,10 @@ extern "C" int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias,
     CUtensorMap tmB;
     int rc;
     if ((rc = tt_make_tmap_2d(&tmA.m[0], x, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK)) != TT_OK) return rc;
-    if ((rc = tt_make_tmap_2d(&tmB, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128, BK)) != TT_OK) return rc;
+    // 256-wide tiles (two heads per tile) run the tensor core at full rate; 128-wide ones only pay off when the
+    // problem has too few tiles to fill the SMs otherwise
+    const int BN = pick_bn(M, N, sm_count(), false);
+    if ((rc = tt_make_tmap_2d(&tmB, w, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BN, BK)) != TT_OK) return rc;
     GemmParams p;
     default_params(p);
     p.M = M; p.N = N; p.K = K;
@@ -792,6 +814,7 @@ extern "C" int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias,
         p.peer_v[r] = (__nv_bfloat16*)v_ptrs[r];
     }
     p.tiles_m = (M + BM - 1) / BM;
-    p.tiles_n = N / 128;
-    return dispatch<128>(false, false, 5, tmA, tmB, p, sm_count(), (cudaStream_t)stream);
+    p.tiles_n = (N + BN - 1) / BN;
+    return BN == 128 ? dispatch<128>(false, false, 5, tmA, tmB, p, sm_count(), (cudaStream_t)stream)
+                     : dispatch<256>(false, false, 5, tmA, tmB, p, sm_count(), (cudaStream_t)stream);
 }
