@@ -149,7 +149,9 @@ def producer_loop(pairs: List[CommPair], iterators: Dict[int, object], encode: C
                   start_seq: Dict[int, int], max_items: Optional[int] = None, idle_sleep: float = 0.002,
                   drop: Optional[Callable[[int, int], bool]] = None, stall_timeout: Optional[float] = None) -> Dict[int, int]:
     """Round-robin service of all consumers: keep up to ``QUEUE_DEPTH`` encoded samples per consumer and
-    one outstanding ``isend`` each.  ``drop(consumer, seq)`` is a host-side fault-injection hook for the
+    one outstanding ``isend`` each.  ``iterators[c]`` yields the samples of this producer's lane only and
+    ``start_seq[c]`` is the lane's first sequence number; consecutive items are ``lanes`` sequence numbers apart.
+    ``drop(consumer, seq)`` is a host-side fault-injection hook for the
     tests (a message that is encoded but never sent).  A consumer whose receive does not match a send within
     ``stall_timeout`` seconds is taken for lost and no longer served, so one dead DiT block cannot starve the
     others.  Returns the number of messages sent per consumer."""
@@ -181,7 +183,7 @@ def producer_loop(pairs: List[CommPair], iterators: Dict[int, object], encode: C
                     exhausted.add(c)
                     continue
                 queues[c].append((seq[c], encode(sample, seq[c])))
-                seq[c] += 1
+                seq[c] += p.lanes                       # the consumer's other producers carry the sequence numbers in between
                 produced[c] += 1
                 progress = True
             if queues[c] and len(inflight[c]) < MAX_OUTSTANDING_SENDS:
@@ -219,77 +221,102 @@ def producer_process(args, train_valid_test_datasets_provider: Callable, encoder
     for p, t, r in reqs:
         r.wait(args.distributed_timeout_minutes * 60.0, f"handshake from consumer {p.consumer}")
         start[p.consumer] = int(t.item())
-    iterators = {}
+    iterators, first, count = {}, {}, 0
     for p in pairs:
-        args.consumed_train_samples = start[p.consumer] * args.global_batch_size
+        # Sample q of consumer d is dataset item q * dp + d.  A producer that carries lane l of L lanes serves
+        # q = l, l + L, ... which is exactly the shard (rank l * dp + d of L * dp) of a data-parallel sampler, so the
+        # samples of the other lanes are never materialised here.
+        begin = start[p.consumer]
+        q0 = begin + ((p.lane - begin) % p.lanes)
+        end = max(begin, args.train_iters * args.num_microbatches)
+        args.consumed_train_samples = (q0 - p.lane) // p.lanes * (p.lanes * p.dp_size) * args.micro_batch_size
         it, _, _ = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args,
-                                                         dp_rank=p.dp_rank, dp_size=p.dp_size)
+                                                         dp_rank=p.lane * p.dp_size + p.dp_rank, dp_size=p.lanes * p.dp_size)
         iterators[p.consumer] = it
-    remaining = max(0, args.train_iters - min(start.values())) * args.num_microbatches
-    producer_loop(pairs, iterators, lambda s, q: encode_sample(s, enc, spec, q, device), start, max_items=remaining)
+        first[p.consumer] = q0
+        count = max(count, len(range(q0, end, p.lanes)))
+    producer_loop(pairs, iterators, lambda s, q: encode_sample(s, enc, spec, q, device), first, max_items=count)
+
+
+class _Lane:
+    """Receive state of one producer feeding this consumer."""
+
+    def __init__(self, pair: CommPair, numel: int, device):
+        self.pair = pair
+        self.bufs = [torch.empty(numel, dtype=torch.bfloat16, device=device) for _ in range(2)]
+        self.slot = 0
+        self.req = None
+        self.to_post = None         # receives still to post (None = unbounded)
 
 
 class EncoderConsumer:
-    """DiT-side endpoint: double-buffered receive, one message always in flight ahead of use."""
+    """DiT-side endpoint: double-buffered receive per producer, one message per producer always in flight ahead of use.
 
-    def __init__(self, pair: CommPair, args=None, device=None, spec: Optional[MessageSpec] = None,
+    ``pair`` is one :class:`CommPair` or the list of this rank's pairs (``parallel.state.get_consumer_pairs()``):
+    with several producers, sample ``seq`` arrives from the producer whose lane is ``seq % lanes``."""
+
+    def __init__(self, pair, args=None, device=None, spec: Optional[MessageSpec] = None,
                  timeout: Optional[float] = None, fallback: Optional[Callable[[], Dict]] = None):
-        self.pair = pair
+        pairs = sorted(pair, key=lambda p: p.lane) if isinstance(pair, (list, tuple)) else [pair]
+        if [p.lane for p in pairs] != list(range(len(pairs))) or any(p.lanes != len(pairs) for p in pairs):
+            raise ValueError("the consumer's pairs must cover lanes 0 .. lanes-1 exactly once")
+        self.pair = pairs[0]
         self.device = device
         self.spec = spec or spec_from_args(args)
         self.timeout = timeout if timeout is not None else (args.distributed_timeout_minutes * 60.0 if args else None)
         self.fallback = fallback
-        self._bufs = [torch.empty(self.spec.numel, dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self._slot = 0
-        self._req = None
+        self._lanes = [_Lane(p, self.spec.numel, device) for p in pairs]
         self._seq = 0
-        self._to_post = None        # receives still to post (None = unbounded)
         self._args = args
         self.bytes_received = 0
 
     def handshake(self, iteration: int, num_messages: Optional[int] = None) -> None:
-        """Tell the producer where to resume; ``num_messages`` bounds how many receives will ever be posted."""
+        """Tell every producer where to resume; ``num_messages`` bounds how many receives will ever be posted."""
         t = torch.tensor([iteration], dtype=torch.int64, device=self.device)
-        dist.isend(t, dst=self.pair.producer).wait()
+        for lane in self._lanes:
+            dist.isend(t, dst=lane.pair.producer).wait()
         self._seq = iteration
-        if num_messages is not None:
-            self._to_post = num_messages
-        elif self._args is not None:
+        if num_messages is None and self._args is not None:
             # never leave an unmatched receive behind at shutdown
-            self._to_post = max(0, self._args.train_iters - iteration) * self._args.num_microbatches
-        self._post()
+            num_messages = max(0, self._args.train_iters - iteration) * self._args.num_microbatches
+        n = len(self._lanes)
+        for i, lane in enumerate(self._lanes):
+            if num_messages is not None:
+                lane.to_post = sum(1 for q in range(iteration, iteration + num_messages) if q % n == i)
+            self._post(lane)
 
-    def _post(self):
-        if self._to_post is not None:
-            if self._to_post <= 0:
-                self._req = None
+    def _post(self, lane: _Lane) -> None:
+        if lane.to_post is not None:
+            if lane.to_post <= 0:
+                lane.req = None
                 return
-            self._to_post -= 1
-        self._req = _Request(dist.irecv(self._bufs[self._slot], src=self.pair.producer))
+            lane.to_post -= 1
+        lane.req = _Request(dist.irecv(lane.bufs[lane.slot], src=lane.pair.producer))
 
     def next_batch(self) -> Dict[str, torch.Tensor]:
-        """The sample for this step; immediately re-posts the receive for the next one."""
-        if self._req is None:
-            self._post()
-        if self._req is None:
+        """The sample for this step; immediately re-posts the receive for that producer's next one."""
+        lane = self._lanes[self._seq % len(self._lanes)]
+        if lane.req is None:
+            self._post(lane)
+        if lane.req is None:
             raise RuntimeError("the encoder stream is exhausted (all scheduled samples were received)")
         try:
-            self._req.wait(self.timeout, f"sample {self._seq} from encoder rank {self.pair.producer}")
-            msg = self._bufs[self._slot]
-            out = unpack_message(self.spec, msg, expect_seq=self._seq)
+            lane.req.wait(self.timeout, f"sample {self._seq} from encoder rank {lane.pair.producer}")
+            out = unpack_message(self.spec, lane.bufs[lane.slot], expect_seq=self._seq)
         except (EncoderTimeout, ProtocolError):
             if self.fallback is None:
                 raise
-            self._req = None
+            lane.req = None
             self._seq += 1
             return self.fallback()
         self.bytes_received += self.spec.nbytes
         self._seq += 1
-        self._slot ^= 1
-        self._post()                      # prefetch: lands while this step computes
+        lane.slot ^= 1
+        self._post(lane)                  # prefetch: lands while this step computes
         out.pop("seq")
         out.pop("text_len")
         return out
 
     def close(self):
-        self._req = None
+        for lane in self._lanes:
+            lane.req = None

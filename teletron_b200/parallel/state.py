@@ -32,11 +32,16 @@ import torch.distributed as dist
 
 @dataclasses.dataclass
 class CommPair:
-    """One encoder-rank -> DiT-rank stream (``parallel_state.py:27-32``)."""
+    """One encoder-rank -> DiT-rank stream (``parallel_state.py:27-32``).
+
+    ``lane`` / ``lanes``: when there are more encoder ranks than consumers, a consumer is fed by ``lanes`` producers in
+    turn; this pair carries the samples whose sequence number is ``lane`` modulo ``lanes``."""
     producer: int
     consumer: int
     dp_rank: int
     dp_size: int
+    lane: int = 0
+    lanes: int = 1
 
 
 @dataclasses.dataclass
@@ -98,16 +103,24 @@ def build_comm_pairs(dit_world: int, encoder_world: int, tp: int, cp: int) -> Li
 
     The consumers are the first rank of every TP x CP block (one per data-parallel
     replica); consumer ``i`` is served by encoder rank ``dit_world + i % encoder_world``.
+    With more encoder ranks than consumers (the reference would leave the extra ones idle)
+    encoder rank ``e`` joins consumer ``e % dp`` and the consumer's samples are dealt out to
+    its producers in turn, so the VAE of several encoder GPUs works for one DiT group.
     """
     if encoder_world == 0:
         return []
     block = tp * cp
     dp = dit_world // block
     pairs = []
+    if encoder_world <= dp:
+        for d in range(dp):
+            pairs.append(CommPair(producer=dit_world + d % encoder_world, consumer=d * block, dp_rank=d, dp_size=dp))
+        return pairs
     for d in range(dp):
-        consumer = d * block
-        pairs.append(CommPair(producer=dit_world + d % encoder_world, consumer=consumer,
-                              dp_rank=d, dp_size=dp))
+        mine = [e for e in range(encoder_world) if e % dp == d]
+        for lane, e in enumerate(mine):
+            pairs.append(CommPair(producer=dit_world + e, consumer=d * block, dp_rank=d, dp_size=dp,
+                                  lane=lane, lanes=len(mine)))
     return pairs
 
 
@@ -274,6 +287,11 @@ def get_comm_pair() -> Optional[CommPair]:
         if p.consumer == _STATE.rank:
             return p
     return None
+
+
+def get_consumer_pairs() -> List[CommPair]:
+    """Every stream this DiT rank consumes from, ordered by lane (empty for non-src ranks)."""
+    return sorted((p for p in _STATE.comm_pairs if p.consumer == _STATE.rank), key=lambda p: p.lane)
 
 
 def get_producer_pairs() -> List[CommPair]:

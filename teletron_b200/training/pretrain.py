@@ -285,9 +285,9 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     train_it = None
     if args.distributed_vae:
         from ..encoder_service import EncoderConsumer
-        pair = ps.get_comm_pair()
-        if pair is not None:
-            consumer = EncoderConsumer(pair, args, device=args.device)
+        pairs = ps.get_consumer_pairs()
+        if pairs:
+            consumer = EncoderConsumer(pairs, args, device=args.device)
             consumer.handshake(args.iteration)
     else:
         timers("train/valid/test-data-iterators-setup", log_level=0).start()

@@ -101,7 +101,46 @@ def test_dropped_message_is_detected_and_falls_back():
     assert res[0][2] is True
 
 
-def _train_with_encoder_rank(rank, world, tmp):
+def _two_producers(rank, world, n_items, start_iter):
+    """rank 0: consumer fed by ranks 1 and 2 in turn (more encoder ranks than DiT groups)."""
+    from teletron_b200.encoder_service import EncoderConsumer, pack_message, producer_loop
+    from teletron_b200.parallel.state import build_comm_pairs
+    import torch.distributed as dist
+    spec = _spec()
+    pairs = build_comm_pairs(1, 2, 1, 1)
+    assert [(p.producer, p.lane, p.lanes) for p in pairs] == [(1, 0, 2), (2, 1, 2)]
+
+    def sample(seq):
+        g = torch.Generator().manual_seed(seq)
+        return (torch.randn(3 + seq % 4, 16, generator=g).bfloat16(), torch.randn(4, generator=g).bfloat16(),
+                torch.randn(16, 1, 4, 8, generator=g).bfloat16(), torch.randn(16, 3, 4, 8, generator=g).bfloat16())
+    if rank > 0:
+        mine = [p for p in pairs if p.producer == rank]
+        t = torch.zeros(1, dtype=torch.int64)
+        dist.irecv(t, src=0).wait()
+        start = int(t)
+        lane, lanes = mine[0].lane, mine[0].lanes
+        q0 = start + ((lane - start) % lanes)
+        items = range(q0, start + n_items, lanes)          # this lane's sequence numbers
+        sent = producer_loop(mine, {0: iter(items)}, lambda s, seq: pack_message(spec, seq, *sample(seq)), {0: q0},
+                             max_items=len(items))
+        return sent[0]
+    cons = EncoderConsumer(pairs, None, device=torch.device("cpu"), spec=spec, timeout=20.0)
+    cons.handshake(start_iter, num_messages=n_items)
+    for i in range(n_items):
+        b = cons.next_batch()
+        assert torch.equal(b["latents"][0], sample(start_iter + i)[3]), i
+    cons.close()
+    return cons.bytes_received
+
+
+def test_two_encoder_ranks_feed_one_consumer_in_turn():
+    res = run_distributed(_two_producers, 3, 7, 41)
+    # sequence numbers 41 .. 47: the odd ones (lane 1) come from rank 2, the even ones from rank 1
+    assert res[0] == 7 * _spec().nbytes and res[1] == 3 and res[2] == 4
+
+
+def _train_with_encoder_rank(rank, world, tmp, enc=1):
     import importlib
     import sys
     sys.path.insert(0, EXAMPLE)
@@ -112,7 +151,7 @@ def _train_with_encoder_rank(rank, world, tmp):
     log = os.path.join(tmp, "log.jsonl")
     argv = ["--model-size", "tiny", "--dataset-type", "FakeDataset", "--num-frames", "9", "--video-resolution", "64", "64",
             "--text-len", "16", "--train-iters", "3", "--lr", "1e-4", "--use-distributed-optimizer", "--num-workers", "0",
-            "--context-parallel-size", "2", "--distributed-vae", "--distributed-vae-world-size", "1",
+            "--context-parallel-size", "2", "--distributed-vae", "--distributed-vae-world-size", str(enc),
             "--encoder-preset", "tiny", "--encoder-max-text-len", "16", "--jsonl-log", log, "--distributed-timeout-minutes", "2"]
     model = pretrain(entry.train_valid_test_datasets_provider, entry.model_provider, entry.forward_step,
                      producer_process=entry.producer_process, extra_args_provider=entry.extra_args_provider, argv=argv)
@@ -123,5 +162,13 @@ def test_training_entry_with_one_encoder_rank(tmp_path):
     """3 CPU ranks: 2 DiT ranks (cp = 2) + 1 encoder rank running the tiny VAE / LLaMA / CLIP and streaming samples."""
     res = run_distributed(_train_with_encoder_rank, 3, str(tmp_path), timeout=420)
     assert res == ["dit", "dit", "encoder"]
+    lines = [json.loads(l) for l in open(tmp_path / "log.jsonl")]
+    assert len(lines) == 3 and all(l["loss"] == l["loss"] for l in lines)
+
+
+def test_training_entry_with_two_encoder_ranks_for_one_dit_group(tmp_path):
+    """4 CPU ranks: 2 DiT ranks (cp = 2, one data-parallel replica) fed by 2 encoder ranks in turn."""
+    res = run_distributed(_train_with_encoder_rank, 4, str(tmp_path), 2, timeout=420)
+    assert res == ["dit", "dit", "encoder", "encoder"]
     lines = [json.loads(l) for l in open(tmp_path / "log.jsonl")]
     assert len(lines) == 3 and all(l["loss"] == l["loss"] for l in lines)
