@@ -190,7 +190,7 @@ def producer_loop(pairs: List[CommPair], iterators: Dict[int, object], encode: C
                 s, msg = queues[c].popleft()
                 if drop is not None and drop(c, s):
                     continue
-                inflight[c].append((_Request(dist.isend(msg, dst=c)), msg, time.monotonic()))
+                inflight[c].append((_Request(dist.isend(msg, dst=c, group=p.group)), msg, time.monotonic()))
                 sent[c] += 1
                 progress = True
         done = all(c in lost or ((c in exhausted or (max_items is not None and produced[c] >= max_items))
@@ -217,7 +217,7 @@ def producer_process(args, train_valid_test_datasets_provider: Callable, encoder
     reqs = []
     for p in pairs:
         t = torch.zeros(1, dtype=torch.int64, device=device)
-        reqs.append((p, t, _Request(dist.irecv(t, src=p.consumer))))
+        reqs.append((p, t, _Request(dist.irecv(t, src=p.consumer, group=p.group))))
     for p, t, r in reqs:
         r.wait(args.distributed_timeout_minutes * 60.0, f"handshake from consumer {p.consumer}")
         start[p.consumer] = int(t.item())
@@ -274,7 +274,7 @@ class EncoderConsumer:
         """Tell every producer where to resume; ``num_messages`` bounds how many receives will ever be posted."""
         t = torch.tensor([iteration], dtype=torch.int64, device=self.device)
         for lane in self._lanes:
-            dist.isend(t, dst=lane.pair.producer).wait()
+            dist.isend(t, dst=lane.pair.producer, group=lane.pair.group).wait()
         self._seq = iteration
         if num_messages is None and self._args is not None:
             # never leave an unmatched receive behind at shutdown
@@ -291,7 +291,7 @@ class EncoderConsumer:
                 lane.req = None
                 return
             lane.to_post -= 1
-        lane.req = _Request(dist.irecv(lane.bufs[lane.slot], src=lane.pair.producer))
+        lane.req = _Request(dist.irecv(lane.bufs[lane.slot], src=lane.pair.producer, group=lane.pair.group))
 
     def next_batch(self) -> Dict[str, torch.Tensor]:
         """The sample for this step; immediately re-posts the receive for that producer's next one."""

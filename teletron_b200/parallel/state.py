@@ -42,6 +42,7 @@ class CommPair:
     dp_size: int
     lane: int = 0
     lanes: int = 1
+    group: Optional[object] = dataclasses.field(default=None, compare=False, repr=False)   # two-rank process group of this stream
 
 
 @dataclasses.dataclass
@@ -183,6 +184,10 @@ def initialize_model_parallel(tensor_model_parallel_size: int = 1, context_paral
         c = rank_coords(rank, tp, cp)
         st.tp_rank, st.cp_rank, st.dp_rank = c["tp"], c["cp"], c["dp"]
     st.comm_pairs = build_comm_pairs(dit_world, encoder_world_size, tp, cp)
+    # every stream gets its own two-rank group: point-to-point traffic on the world communicator would be serialised
+    # with everything else issued on it (and, with NCCL's eager initialisation, is treated like a collective)
+    for pair in st.comm_pairs:
+        pair.group = _new_group([pair.consumer, pair.producer], timeout=timeout)
     st.initialized = True
     _STATE = st
 

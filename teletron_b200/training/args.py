@@ -70,6 +70,8 @@ def _add_train_args(p):
     g.add_argument("--data-parallel-random-init", action="store_true")
     g.add_argument("--exit-interval", type=int, default=None)
     g.add_argument("--step-timeout-seconds", type=float, default=0.0, help="watchdog: abort if a step takes longer (0 = off)")
+    g.add_argument("--hang-dump-seconds", type=float, default=0.0,
+                   help="every N seconds, dump the Python stack of every thread of every rank to stderr (0 = off): shows where a rank sits when a job stalls")
 
 
 def _add_parallel_args(p):

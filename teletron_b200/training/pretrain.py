@@ -64,6 +64,9 @@ def initialize(extra_args_provider: Optional[Callable] = None, argv=None, args_d
     args = args_mod.validate_args(args)
     args_mod.set_args(args)
     _TIMERS = Timers(args.timing_log_level, args.timing_log_option)
+    if args.hang_dump_seconds > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(args.hang_dump_seconds, repeat=True)
     use_cuda = torch.cuda.is_available()
     if use_cuda:
         torch.cuda.set_device(args.local_rank % torch.cuda.device_count())
