@@ -73,7 +73,11 @@ def initialize(extra_args_provider: Optional[Callable] = None, argv=None, args_d
     if args.world_size > 1 and not dist.is_initialized():
         backend = args.distributed_backend or ("nccl" if use_cuda else "gloo")
         kw = {}
-        if use_cuda and backend == "nccl":
+        # Eager NCCL initialisation (communicators split from the world one) is used unless encoder ranks stream to DiT
+        # ranks: with it, point-to-point calls run on the group's collective communicator, and a two-rank stream group
+        # that is not the whole world failed there ("Send: invalid root"); lazily initialised groups give every
+        # send/recv pair its own two-rank communicator, the long-standing path.
+        if use_cuda and backend == "nccl" and not args.distributed_vae:
             kw["device_id"] = torch.device("cuda", torch.cuda.current_device())
         dist.init_process_group(backend=backend, world_size=args.world_size, rank=args.rank,
                                 timeout=datetime.timedelta(minutes=args.distributed_timeout_minutes), **kw)
