@@ -74,7 +74,8 @@ def test_rank_lists_follow_tp_cp_dp_order():
     assert L["tp_cp"] == [[0, 1, 2, 3], [4, 5, 6, 7]]
     assert rank_coords(6, 2, 2) == {"tp": 0, "cp": 1, "dp": 1}
     pairs = build_comm_pairs(6, 2, 2, 3)            # 6 DiT ranks (tp2 cp3 -> dp1) + 2 encoder ranks
-    assert [(p.producer, p.consumer) for p in pairs] == [(6, 0)]
+    # more encoder ranks than DiT groups: both feed the one consumer in turn (the reference would leave rank 7 idle)
+    assert [(p.producer, p.consumer, p.lane, p.lanes) for p in pairs] == [(6, 0, 0, 2), (7, 0, 1, 2)]
     pairs = build_comm_pairs(8, 2, 1, 2)            # dp 4, two producers
     assert [(p.producer, p.consumer, p.dp_rank) for p in pairs] == [(8, 0, 0), (9, 2, 1), (8, 4, 2), (9, 6, 3)]
     with pytest.raises(ValueError):
