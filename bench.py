@@ -120,6 +120,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _heap_bytes() -> int:
+    from teletron_b200.parallel import symm_mem
+    return int(symm_mem.ALLOCATED_BYTES)
+
+
 def main():
     a = parse()
     if a.impl == "reference":
@@ -270,7 +275,10 @@ def main():
                "model_tflops_per_gpu": flops * value / a.gpus / 1e12, "clocks": clocks, "e2e": e2e,
                "gpu_launches": launches,
                "kernel_backends": {"gemm": dict(gemm_mod.COUNTERS), "attention": dict(attn_mod.COUNTERS)},
-               "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
+               # the symmetric heaps (parameter / gradient buffers and collective workspaces of the fused-collective mode)
+               # are raw device allocations that the PyTorch allocator's peak does not see
+               "peak_mem_gb": (torch.cuda.max_memory_allocated() + _heap_bytes()) / 2 ** 30,
+               "peak_mem_torch_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
         print(json.dumps(out), flush=True)
     if dist.is_initialized():
         dist.barrier()

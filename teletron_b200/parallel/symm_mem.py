@@ -36,6 +36,9 @@ def _as_tensor(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
     return torch.as_tensor(_RawBuffer(ptr, nbytes), device=device)
 
 
+ALLOCATED_BYTES = 0      # bytes of symmetric heaps this process holds (outside the PyTorch caching allocator)
+
+
 class SymmetricHeap:
     """One slab per rank; ``alloc`` hands out identically placed regions (bump allocator, 1 KiB aligned)."""
 
@@ -48,6 +51,8 @@ class SymmetricHeap:
         p = ctypes.c_void_p()
         call("tt_symm_alloc", ctypes.c_size_t(self.nbytes), ctypes.byref(p))
         self.local_ptr = p.value
+        global ALLOCATED_BYTES
+        ALLOCATED_BYTES += self.nbytes
         self.peer_ptrs: List[int] = [0] * self.world
         self.peer_ptrs[self.rank] = self.local_ptr
         self._opened: List[int] = []
@@ -125,6 +130,8 @@ class SymmetricHeap:
         if self.local_ptr:
             call("tt_symm_free", ctypes.c_void_p(self.local_ptr))
             self.local_ptr = 0
+            global ALLOCATED_BYTES
+            ALLOCATED_BYTES -= self.nbytes
 
 
 _HEAPS: Dict[int, SymmetricHeap] = {}
