@@ -23,6 +23,7 @@ import torch
 from torch import nn
 from torch.utils.checkpoint import checkpoint
 
+from ... import ops
 from ...parallel import mappings as M
 from ...parallel import state as ps
 from ...parallel.pad import SeqPad
@@ -169,8 +170,10 @@ class HunyuanVideoTransformer3DModel(nn.Module):
             x = M.scatter_to_sequence_parallel_region(x, tp_group, dim=1)
             ctx = M.scatter_to_sequence_parallel_region(ctx, tp_group, dim=1)
 
-        x, ctx = self._run_blocks(self.transformer_blocks, x, ctx, temb, cos, sin, pad, kv_valid_len)
-        x, ctx = self._run_blocks(self.single_transformer_blocks, x, ctx, temb, cos, sin, pad, kv_valid_len)
+        with ops.nvtx_range("dual_blocks"):
+            x, ctx = self._run_blocks(self.transformer_blocks, x, ctx, temb, cos, sin, pad, kv_valid_len)
+        with ops.nvtx_range("single_blocks"):
+            x, ctx = self._run_blocks(self.single_transformer_blocks, x, ctx, temb, cos, sin, pad, kv_valid_len)
 
         if sp:
             # everything after the blocks is replicated over TP: every rank holds the full gradient of the gathered rows

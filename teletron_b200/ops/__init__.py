@@ -37,6 +37,28 @@ def get_impl() -> str:
     return _IMPL
 
 
+_NVTX = os.environ.get("TELETRON_B200_NVTX", "0") == "1"
+
+
+def set_nvtx(enabled: bool) -> None:
+    """Named ranges around blocks and steps for a timeline profiler (set by ``--profile``)."""
+    global _NVTX
+    _NVTX = bool(enabled)
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """``torch.cuda.nvtx`` range when enabled and CUDA is present; otherwise free."""
+    if _NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
+
+
 @contextlib.contextmanager
 def impl(name: str):
     prev = get_impl()

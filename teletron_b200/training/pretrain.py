@@ -30,6 +30,7 @@ from . import args as args_mod
 from .checkpoint import load_checkpoint, save_checkpoint
 from .logging import MetricLogger, Timers, model_flops_per_sample, peak_bf16_tflops, print_rank_0
 from .optimizer import DistributedOptimizer, OptimizerParamScheduler
+from ..ops import nvtx_range
 from .watchdog import StepWatchdog
 
 _TIMERS: Optional[Timers] = None
@@ -136,19 +137,23 @@ def train_step(forward_step_func, data_iterator, model: DistributedDataParallel,
         ctx = model.no_sync() if i < n_mb - 1 else _nullcontext()
         with ctx:
             timers("forward", log_level=1).start()
-            out, loss_func = forward_step_func(data_iterator, model)
-            loss, reduced = loss_func(out)
+            with nvtx_range("forward"):
+                out, loss_func = forward_step_func(data_iterator, model)
+                loss, reduced = loss_func(out)
             timers("forward").stop()
             timers("backward", log_level=1).start()
-            (loss / n_mb).backward()
+            with nvtx_range("backward"):
+                (loss / n_mb).backward()
             timers("backward").stop()
         for k, v in reduced.items():
             losses.setdefault(k, []).append(v.detach() if torch.is_tensor(v) else torch.tensor(v))
     timers("grad-sync", log_level=1).start()
-    model.finish_grad_sync()
+    with nvtx_range("grad-sync"):
+        model.finish_grad_sync()
     timers("grad-sync").stop()
     timers("optimizer", log_level=1).start()
-    ok = optimizer.step()
+    with nvtx_range("optimizer"):
+        ok = optimizer.step()
     timers("optimizer").stop()
     if ok:
         scheduler.step(1)
@@ -187,6 +192,8 @@ def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, a
     skipped_total = 0
     while iteration < args.train_iters:
         if args.profile and use_cuda and iteration == args.profile_step_start and args.rank in args.profile_ranks:
+            from .. import ops as _ops
+            _ops.set_nvtx(True)
             torch.cuda.cudart().cudaProfilerStart()
         if watchdog:
             watchdog.beat(iteration)
@@ -240,6 +247,8 @@ def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, a
             save_checkpoint(iteration, model, optimizer, scheduler, args, _step_state(model))
         if args.profile and use_cuda and iteration == args.profile_step_end and args.rank in args.profile_ranks:
             torch.cuda.cudart().cudaProfilerStop()
+            from .. import ops as _ops
+            _ops.set_nvtx(False)
         if args.exit_interval and iteration % args.exit_interval == 0:
             break
     if watchdog:
