@@ -90,11 +90,14 @@ def forward_step(data_iterator, model):
 def train_valid_test_datasets_provider(train_val_test_num_samples):
     args = get_args()
     tiny = args.model_size == "tiny"
-    ds = build_dataset(args.dataset_type, num_frames=args.num_frames, video_resolution=args.video_resolution,
-                       koala_opt=args.koala_opt, text_len=args.text_len,
-                       text_dim=64 if tiny else 4096, pooled_dim=32 if tiny else 768,
-                       with_pixels=bool(args.with_vae or args.distributed_vae))
-    return ds, None, None
+    kw = dict(num_frames=args.num_frames, video_resolution=args.video_resolution, koala_opt=args.koala_opt,
+              text_len=args.text_len, text_dim=64 if tiny else 4096, pooled_dim=32 if tiny else 768,
+              with_pixels=bool(args.with_vae or args.distributed_vae))
+    ds = build_dataset(args.dataset_type, **kw)
+    valid = None
+    if args.eval_iters > 0 and args.dataset_type == "FakeDataset":
+        valid = build_dataset(args.dataset_type, seed=1, **kw)        # held-out synthetic items
+    return ds, valid, None
 
 
 if __name__ == "__main__":

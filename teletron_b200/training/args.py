@@ -145,6 +145,9 @@ def _add_io_args(p):
     g.add_argument("--log-interval", type=int, default=1)
     g.add_argument("--tensorboard-dir", type=str, default=None)
     g.add_argument("--tensorboard-queue-size", type=int, default=10)
+    g.add_argument("--wandb-project", type=str, default=None, help="log to Weights & Biases when the package is installed")
+    g.add_argument("--wandb-exp-name", type=str, default=None)
+    g.add_argument("--wandb-save-dir", type=str, default=None)
     g.add_argument("--jsonl-log", type=str, default=None)
     g.add_argument("--timing-log-level", type=int, default=0, choices=[0, 1, 2])
     g.add_argument("--timing-log-option", type=str, default="minmax", choices=["max", "minmax", "all"])

@@ -149,8 +149,19 @@ def model_flops_per_sample(num_params_blocks: int, video_tokens: int, text_token
 
 
 class MetricLogger:
-    def __init__(self, jsonl_path: Optional[str] = None, tensorboard_dir: Optional[str] = None, queue_size: int = 10):
+    def __init__(self, jsonl_path: Optional[str] = None, tensorboard_dir: Optional[str] = None, queue_size: int = 10,
+                 wandb_project: Optional[str] = None, wandb_name: Optional[str] = None, wandb_dir: Optional[str] = None,
+                 config: Optional[dict] = None):
         self.jsonl = None
+        self.wandb = None
+        if wandb_project and is_rank_0():
+            try:
+                import wandb
+                wandb.init(project=wandb_project, name=wandb_name, dir=wandb_dir,
+                           config={k: v for k, v in (config or {}).items() if isinstance(v, (int, float, str, bool, type(None)))})
+                self.wandb = wandb
+            except Exception as e:      # wandb is optional
+                print_rank_0(f"wandb unavailable ({e}); logging to stdout/JSONL only")
         if jsonl_path and is_rank_0():
             os.makedirs(os.path.dirname(os.path.abspath(jsonl_path)), exist_ok=True)
             self.jsonl = open(jsonl_path, "a")
@@ -172,12 +183,16 @@ class MetricLogger:
             for k, v in metrics.items():
                 if isinstance(v, (int, float)):
                     self.tb.add_scalar(k, v, step)
+        if self.wandb is not None:
+            self.wandb.log({k: v for k, v in metrics.items() if isinstance(v, (int, float))}, step=step)
 
     def close(self):
         if self.jsonl is not None:
             self.jsonl.close()
         if self.tb is not None:
             self.tb.close()
+        if self.wandb is not None:
+            self.wandb.finish()
 
 
 def peak_bf16_tflops() -> float:

@@ -17,7 +17,7 @@ import datetime
 import os
 import random
 import time
-from typing import Callable, Optional
+from typing import Callable, Dict, Optional
 
 import numpy as np
 import torch
@@ -28,7 +28,7 @@ from ..parallel import state as ps
 from ..parallel.grad_buffer import DistributedDataParallel
 from . import args as args_mod
 from .checkpoint import load_checkpoint, save_checkpoint
-from .logging import MetricLogger, Timers, model_flops_per_sample, peak_bf16_tflops, print_rank_0
+from .logging import MetricLogger, Timers, model_flops_per_sample, peak_bf16_tflops, print_rank_0, print_rank_last
 from .optimizer import DistributedOptimizer, OptimizerParamScheduler
 from ..ops import nvtx_range
 from .watchdog import StepWatchdog
@@ -179,9 +179,46 @@ def average_losses_across_data_parallel_group(losses):
     return t
 
 
-def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, args, on_step_end=None):
+def evaluate(forward_step_func, data_iterator, model, args, max_iters: Optional[int] = None) -> Dict[str, float]:
+    """Mean of the reduced losses over ``eval_iters`` forward passes without gradients (the reference gets this loop from
+    Megatron's ``evaluate_and_print_results``; its scripts set the interval so high that it never runs)."""
+    n = args.eval_iters if max_iters is None else max_iters
+    was_training = model.training
+    model.eval()
+    sums: Dict[str, float] = {}
+    done = 0
+    # the diffusion wrapper draws its noise from (seed, step): validation must not advance the training stream
+    inner = model.module if hasattr(model, "module") else model
+    saved_step = getattr(inner, "step", None)
+    if saved_step is not None:
+        inner.step = 1_000_000_007        # a fixed stream of its own: every validation sees the same noise and timesteps
+    with torch.no_grad():
+        for _ in range(n):
+            try:
+                out, loss_func = forward_step_func(data_iterator, model)
+            except StopIteration:
+                break
+            _, reduced = loss_func(out)
+            for k, v in reduced.items():
+                sums[k] = sums.get(k, 0.0) + float(v)
+            done += 1
+    if saved_step is not None:
+        inner.step = saved_step
+    if was_training:
+        model.train()
+    return {k: v / max(1, done) for k, v in sums.items()}
+
+
+def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, args, on_step_end=None,
+          valid_data_iterator=None, do_valid: Optional[bool] = None):
+    """``do_valid``: whether a validation set exists; only the source rank of each TP x CP block holds the iterator, so
+    the other ranks (which take part through the batch broadcast) must be told."""
+    if do_valid is None:
+        do_valid = valid_data_iterator is not None
     timers = get_timers()
-    logger = MetricLogger(args.jsonl_log, args.tensorboard_dir, args.tensorboard_queue_size)
+    logger = MetricLogger(args.jsonl_log, args.tensorboard_dir, args.tensorboard_queue_size,
+                          wandb_project=getattr(args, "wandb_project", None), wandb_name=getattr(args, "wandb_exp_name", None),
+                          wandb_dir=getattr(args, "wandb_save_dir", None), config=vars(args))
     watchdog = StepWatchdog(args.step_timeout_seconds) if args.step_timeout_seconds > 0 else None
     model.train()
     iteration = args.iteration
@@ -241,6 +278,13 @@ def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, a
             logger.log(iteration, metrics)
             if args.timing_log_level > 0:
                 timers.log(normalizer=args.log_interval)
+        if do_valid and args.eval_iters > 0 and args.eval_interval and iteration % args.eval_interval == 0:
+            timers("evaluate", log_level=0).start()
+            val = evaluate(forward_step_func, valid_data_iterator, model, args)
+            timers("evaluate").stop()
+            line = f" validation loss at iteration {iteration} | " + " | ".join(f"{k}: {v:.6E}" for k, v in val.items())
+            print_rank_last(line)
+            logger.log(iteration, {f"valid_{k}": v for k, v in val.items()})
         if on_step_end is not None:
             on_step_end(iteration, losses)
         if args.save and args.save_interval and iteration % args.save_interval == 0:
@@ -298,7 +342,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     print_rank_0(f"time to initialize (seconds): {time.time() - float(start):.3f}")
     model, optimizer, scheduler = setup_model_and_optimizer(model_provider, args)
     consumer = None
-    train_it = None
+    train_it = valid_it = None
     if args.distributed_vae:
         from ..encoder_service import EncoderConsumer
         pairs = ps.get_consumer_pairs()
@@ -307,12 +351,16 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             consumer.handshake(args.iteration)
     else:
         timers("train/valid/test-data-iterators-setup", log_level=0).start()
-        train_it, _, _ = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args)
+        train_it, valid_it, _ = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args)
         timers("train/valid/test-data-iterators-setup").stop()
     args.encoder_consumer = consumer
     print_rank_0("done with setup ...")
     print_rank_0("training ...")
-    iteration = train(forward_step_func, model, optimizer, scheduler, train_it, args)
+    do_valid = torch.tensor([1 if valid_it is not None else 0], device=args.device)
+    if dist.is_initialized() and args.dit_world_size > 1:
+        dist.all_reduce(do_valid, op=dist.ReduceOp.MAX, group=ps.get_transformer_model_group())
+    iteration = train(forward_step_func, model, optimizer, scheduler, train_it, args, valid_data_iterator=valid_it,
+                      do_valid=bool(do_valid.item()))
     if args.save and iteration != 0 and (not args.save_interval or iteration % args.save_interval != 0):
         save_checkpoint(iteration, model, optimizer, scheduler, args, _step_state(model))
     if consumer is not None:

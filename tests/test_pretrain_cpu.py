@@ -56,3 +56,16 @@ def test_tp2_matches_cp2_loss_curve(tmp_path):
     lb = [json.loads(l)["loss"] for l in b[0][1].strip().splitlines()]
     for x, y in zip(la, lb):
         assert abs(x - y) < 2e-4 * max(1.0, abs(x))
+
+
+def test_validation_loop_runs_at_the_eval_interval(tmp_path):
+    """--eval-interval / --eval-iters: forward-only passes over a held-out synthetic set, logged next to the training
+    loss, leaving the weights untouched (same final weights as a run without evaluation)."""
+    with_eval = run_distributed(_train, 2, str(tmp_path / "a"), ["--context-parallel-size", "2", "--eval-interval", "2",
+                                                                  "--eval-iters", "2"], 4, False)
+    without = run_distributed(_train, 2, str(tmp_path / "b"), ["--context-parallel-size", "2"], 4, False)
+    lines = [json.loads(l) for l in with_eval[0][1].strip().splitlines()]
+    valid = [l for l in lines if "valid_loss" in l]
+    assert [l["step"] for l in valid] == [2, 4] and all(l["valid_loss"] == l["valid_loss"] for l in valid)
+    assert len([l for l in lines if "loss" in l]) == 4
+    torch.testing.assert_close(with_eval[0][0], without[0][0], rtol=0, atol=0)
