@@ -50,6 +50,8 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-save-attention", action="store_true")
     p.add_argument("--fused-comm", type=int, default=1, help="1: in-kernel NVLink collectives for context parallelism")
+    p.add_argument("--overlap-grad-reduce", type=int, default=0,
+                   help="1: bucketed gradient reduce-scatter on a side stream during backward")
     p.add_argument("--sequence-parallel", type=int, default=0,
                    help="1: shard the residual stream's tokens over the tensor-parallel ranks (all-gather -> GEMM / GEMM -> reduce-scatter)")
     return p.parse_args()
@@ -165,6 +167,8 @@ def main():
         argv += ["--recompute-granularity", "full", "--recompute-method", "block"]
     if a.impl == "ours" and a.fused_comm and a.gpus > 1:
         argv += ["--fused-comm"]
+    if a.overlap_grad_reduce and a.gpus > 1:
+        argv += ["--overlap-grad-reduce"]
     sp = bool(a.sequence_parallel) and tp > 1
     if sp:
         argv += ["--sequence-parallel"]

@@ -47,6 +47,7 @@ class Bucket:
     params: List[nn.Parameter]
     pending: int = 0
     handle: Optional[object] = None
+    late: bool = False          # holds TP-partial gradients: synchronised only after their TP reduction
 
 
 def param_uses_weight_decay(name: str, p: nn.Parameter) -> bool:
@@ -69,7 +70,9 @@ class ParamAndGradBuffer:
         def key(item):
             name, p = item
             dup = not getattr(p, "tensor_model_parallel", False)
-            return (dup, not param_uses_weight_decay(name, p))
+            # parameters whose gradients are partial sums over TP sit at the very end: only the last bucket(s) have to
+            # wait for that reduction when bucket collectives are overlapped with backward
+            return (dup, not param_uses_weight_decay(name, p), bool(getattr(p, "tp_partial_grad", False)))
         ordered = sorted(named_params, key=key)            # stable: keeps model order inside a region
         self.param_index: Dict[nn.Parameter, Tuple[int, int]] = {}
         self.names: Dict[nn.Parameter, str] = {}
@@ -186,9 +189,14 @@ class DistributedDataParallel(nn.Module):
         self._hooks = []
         self.tp_group = tp_group
         self._tp_partial = [p for _, p in named if getattr(p, "tp_partial_grad", False)]
-        if self._tp_partial and self.overlap_grad_reduce:
-            raise ValueError("overlap_grad_reduce is incompatible with tensor-parallel partial gradients; "
-                             "their TP reduction must precede the data-parallel sync")
+        partial = set(self._tp_partial)
+        for buf in self.buffers:
+            for b in buf.buckets:
+                # a bucket that holds TP-partial gradients is synchronised in finish_grad_sync, after their TP reduction
+                b.late = any(p in partial for p in b.params)
+        # with the symmetric heap, overlapped bucket reductions (and every barrier of this heap that belongs to them) run on
+        # one side stream: the barrier's flags only ever grow if the barriers of a heap execute in the order of issue
+        self._side = torch.cuda.Stream() if (self.overlap_grad_reduce and self.heap is not None) else None
         if self.overlap_grad_reduce:
             for buf in self.buffers:
                 for p in buf.params:
@@ -219,7 +227,7 @@ class DistributedDataParallel(nn.Module):
                 return
             for b in buf.param_buckets[p]:
                 b.pending -= 1
-                if b.pending == 0:
+                if b.pending == 0 and not b.late:
                     self._launch(buf, b, async_op=True)
         return hook
 
@@ -233,6 +241,18 @@ class DistributedDataParallel(nn.Module):
             # peers' buckets are read over NVLink and summed in fp32 with the 1/(dp*cp) scale folded in
             from ..ops import fused_comm as FC
             s, e = buf.shard_range(b, self.rank)
+            if self._side is not None:
+                # overlapped with backward: once this bucket's gradients are complete on the compute stream, the side
+                # stream meets the peers at a barrier (their copies of the bucket are complete too) and reduces this
+                # rank's shard.  The shard it writes is the part of this rank's bucket that no peer reads.
+                ready = torch.cuda.Event()
+                ready.record()
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(ready)
+                    self.heap.barrier()
+                    FC.fused_grad_reduce_scatter(self.heap, self.heap_offsets[1], s, e - s, buf.grad_data[s:e], self.grad_scale)
+                b.handle = "fused-side"
+                return
             FC.fused_grad_reduce_scatter(self.heap, self.heap_offsets[1], s, e - s, buf.grad_data[s:e], self.grad_scale)
             b.handle = "fused"
             return
@@ -246,13 +266,25 @@ class DistributedDataParallel(nn.Module):
     def start_grad_sync(self):
         for buf in self.buffers:
             for b in buf.buckets:
-                if b.handle is None:
+                if b.handle is None and not b.late:
                     self._launch(buf, b, async_op=True)
 
     def finish_grad_sync(self):
         """Wait for (or issue) every bucket collective; afterwards each rank's shard holds the
         averaged gradient (ZeRO-1) or the whole buffer does (all-reduce mode)."""
         allreduce_tp_partial_grads(self._tp_partial, self.tp_group)
+        if self._side is not None:
+            # buckets not yet launched (those with TP-partial gradients, or all of them after no_sync micro-batches) go
+            # through the same side-stream path; the closing barrier is issued there as well, then the compute stream joins
+            for buf in self.buffers:
+                for b in buf.buckets:
+                    if b.handle is None:
+                        self._launch(buf, b, async_op=True)
+            with torch.cuda.stream(self._side):
+                self.heap.barrier()    # all peers have read this rank's buckets; they may be overwritten again
+            torch.cuda.current_stream().wait_stream(self._side)
+            self._reset_pending()
+            return
         if self.heap is not None:
             self.heap.barrier()        # every rank's gradients are complete before anyone reads them
         for buf in self.buffers:

@@ -106,7 +106,7 @@ def setup_model_and_optimizer(model_provider: Callable, args):
                                   overlap_grad_reduce=args.overlap_grad_reduce, bucket_bytes=bucket_bytes,
                                   check_for_nan_in_grad=args.check_for_nan_in_loss_and_grad,
                                   tp_group=ps.get_tensor_model_parallel_group(),
-                                  fused_comm=args.fused_comm and not args.overlap_grad_reduce)
+                                  fused_comm=args.fused_comm)
     if args.data_parallel_random_init:
         ddp.broadcast_params()
     master_mode = args.master_weight_mode if args.params_dtype != torch.float32 else "none"

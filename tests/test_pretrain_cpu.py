@@ -69,3 +69,14 @@ def test_validation_loop_runs_at_the_eval_interval(tmp_path):
     assert [l["step"] for l in valid] == [2, 4] and all(l["valid_loss"] == l["valid_loss"] for l in valid)
     assert len([l for l in lines if "loss" in l]) == 4
     torch.testing.assert_close(with_eval[0][0], without[0][0], rtol=0, atol=0)
+
+
+def test_overlapped_grad_reduce_matches_plain_sync(tmp_path):
+    """--overlap-grad-reduce launches each bucket's collective from gradient hooks during backward; buckets that hold
+    tensor-parallel partial gradients wait for their TP reduction.  Same weights as the plain post-backward sync, on
+    tp2 x dp2 with small buckets (several per buffer)."""
+    extra = ["--tensor-model-parallel-size", "2", "--ddp-bucket-size", "40000"]
+    a = run_distributed(_train, 4, str(tmp_path / "a"), extra, 3, False)
+    b = run_distributed(_train, 4, str(tmp_path / "b"), extra + ["--overlap-grad-reduce"], 3, False)
+    for r in range(4):
+        torch.testing.assert_close(a[r][0], b[r][0], rtol=0, atol=0)
