@@ -61,6 +61,8 @@ struct BwdParams {
     int pitch;              // multiple of 64, so every 64-query chunk of statistics is 16-byte aligned
     float scale;            // softmax scale
     int* status;
+    const __nv_bfloat16* q_raw;     // q [BH, S, 128] and dout [B, S, H * 128] as plain pointers: the variant that keeps the
+    const __nv_bfloat16* do_raw;    // stationary operands in tensor memory loads them with ordinary loads
 };
 
 // delta[bh, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head)
@@ -84,7 +86,10 @@ __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restr
     }
 }
 
-template <bool KVS>
+// TSA (query-stationary only): the stationary operands Q and dO live in tensor memory (bf16 pairs, columns [384, 512),
+// free in that kernel) instead of shared memory, so the score-type products become TS instructions.  An SS instruction
+// with N = 128 was measured at ~128 clocks on this part, a TS one at ~84.
+template <bool KVS, bool TSA = false>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
@@ -109,6 +114,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t ds_ready = s_full + 24u;                    // P and dS have been written over dP
     const uint32_t acc_final = s_full + 32u;
 
+    static_assert(!(KVS && TSA), "the key-stationary kernel has no free tensor-memory columns");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
     const int b = bh / p.H, head = bh - b * p.H;
@@ -118,7 +124,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        mbar_init(a_full, 1);
+        mbar_init(a_full, TSA ? 4 * kGroups : 1);
         for (int s = 0; s < kRing1; ++s) {
             mbar_init(b1_full(s), 1);
             mbar_init(b1_empty(s), 1);
@@ -144,13 +150,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
     constexpr uint32_t kT1 = 0, kT2 = 128, kAcc1 = 256, kAcc2 = 384;
+    constexpr uint32_t kA1 = 384, kA2 = 448;          // TSA: Q and dO as bf16 pairs, 64 columns each
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_arrive_expect_tx(a_full, 2 * kTile);
+            if (!TSA) mbar_arrive_expect_tx(a_full, 2 * kTile);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
+                if (TSA) break;
                 if (KVS) {
                     tma_load_3d(sA1 + h * kSlab, &tmK, a_full, h * 64, r0, bh);
                     tma_load_3d(sA2 + h * kSlab, &tmV, a_full, h * 64, r0, bh);
@@ -189,8 +197,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t o = (kk >> 2) * kSlab + (kk & 3) * 32;
-                    umma_bf16_ss(tmem + t_col, smem_desc_sw128(sa + o, 16, 1024), smem_desc_sw128(sb + o, 16, 1024), idesc_t,
-                                 kk ? 1u : 0u);
+                    if (TSA)        // A from tensor memory: eight 32-bit columns per K = 16 step
+                        umma_bf16_ts(tmem + t_col, tmem + (t_col == kT1 ? kA1 : kA2) + kk * 8,
+                                     smem_desc_sw128(sb + o, 16, 1024), idesc_t, kk ? 1u : 0u);
+                    else
+                        umma_bf16_ss(tmem + t_col, smem_desc_sw128(sa + o, 16, 1024), smem_desc_sw128(sb + o, 16, 1024),
+                                     idesc_t, kk ? 1u : 0u);
                 }
             };
             // acc[128 x 128] += A (bf16 pairs in tensor memory, 128 x 128 chunk rows) x chunk (MN-major B)
@@ -262,6 +274,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             my_delta = row_live ? p.delta[(long)bh * p.pitch + row] : 0.f;
         }
         const uint32_t t1 = tmem + lane_sel + kT1 + part * kCols, t2 = tmem + lane_sel + kT2 + part * kCols;
+        if (TSA) {
+            // stationary operands into tensor memory: this thread owns row `srow` and 32 of its 128 elements (16 columns
+            // of bf16 pairs, in memory order: element 2j in the low half of column j)
+            uint32_t qv[16], dv[16];
+            if (row_live) {
+                const uint4* qp = reinterpret_cast<const uint4*>(p.q_raw + ((long)bh * p.S + row) * D + part * 32);
+                const uint4* dp = reinterpret_cast<const uint4*>(p.do_raw + (((long)b * p.S + row) * p.H + head) * D + part * 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint4 a = __ldg(qp + i), g = __ldg(dp + i);
+                    qv[4 * i] = a.x; qv[4 * i + 1] = a.y; qv[4 * i + 2] = a.z; qv[4 * i + 3] = a.w;
+                    dv[4 * i] = g.x; dv[4 * i + 1] = g.y; dv[4 * i + 2] = g.z; dv[4 * i + 3] = g.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) qv[i] = dv[i] = 0u;
+            }
+            tmem_st_32x16(tmem + lane_sel + kA1 + part * 16, qv);
+            tmem_st_32x16(tmem + lane_sel + kA2 + part * 16, dv);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_full);
+        }
         for (int c = 0; c < n_chunks; ++c) {
             const uint32_t par = (uint32_t)c & 1u;
             const int col0 = c * BC + part * kCols;         // first streamed row of this thread's 32 columns
@@ -415,6 +451,8 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
         cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_bwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_record_cuda(e);
         configured = true;
     }
@@ -432,6 +470,8 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     p.pitch = pitch;
     p.scale = scale;
     p.status = status;
+    p.q_raw = (const __nv_bfloat16*)q;
+    p.do_raw = (const __nv_bfloat16*)dout;
     // dK, dV: stationary keys (K, V resident), streamed queries (Q, dO)
     p.out1 = (__nv_bfloat16*)dv;
     p.out2 = (__nv_bfloat16*)dk;
@@ -440,7 +480,12 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     // dQ: stationary queries (Q, dO resident), streamed keys (K, V)
     p.out1 = (__nv_bfloat16*)dq;
     p.out2 = nullptr;
-    attn_bwd_kernel<false><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
+    // TELETRON_B200_ATTN_BWD_TSA=1 selects the variant with Q / dO in tensor memory (off by default)
+    static const bool tsa = [] { const char* v = getenv("TELETRON_B200_ATTN_BWD_TSA"); return v != nullptr && v[0] == '1'; }();
+    if (tsa)
+        attn_bwd_kernel<false, true><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
+    else
+        attn_bwd_kernel<false><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }
