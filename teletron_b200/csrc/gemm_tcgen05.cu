@@ -72,6 +72,7 @@ struct GemmParams {
     const float* sin_t;
     float eps;
     int rope_len, heads_per_rank, s_in, s_out, out_off, only_local;
+    int coalesce;           // EPI 5: stage each warp's 32 x 128 block in shared memory and store 512 contiguous bytes per instruction
     __nv_bfloat16* peer_q[TT_MAX_PEERS];
     __nv_bfloat16* peer_k[TT_MAX_PEERS];
     __nv_bfloat16* peer_v[TT_MAX_PEERS];
@@ -120,6 +121,7 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
     auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::kStages + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::kStages + 2 + b); };
+    const uint32_t epi_stage = bar_base + 256u;      // EPI 5 with coalesced stores: 4 warps x 8 KB (only when launched with room for it)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -346,7 +348,9 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
 #pragma unroll
                     for (int g = 0; g < 16; ++g) tt::st8(arow + g * 8, tt::pack8(v + g * 8));
                 }
-                if (row_ok && (!p.only_local || dest == p.my_rank)) {
+                const bool keep = row_ok && (!p.only_local || dest == p.my_rank);
+                __nv_bfloat16* drow = nullptr;
+                if (keep) {
                     const int b = row / p.s_in, srow = row - b * p.s_in;
                     if (which < 2) {
                         float ss = 0.f;
@@ -376,9 +380,41 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                         }
                     }
                     __nv_bfloat16* dbase = which == 0 ? p.peer_q[dest] : (which == 1 ? p.peer_k[dest] : p.peer_v[dest]);
-                    __nv_bfloat16* drow = dbase + (((long)b * p.heads_per_rank + hl) * p.s_out + p.out_off + srow) * 128;
+                    drow = dbase + (((long)b * p.heads_per_rank + hl) * p.s_out + p.out_off + srow) * 128;
+                }
+                if (!p.coalesce) {
+                    if (keep) {
 #pragma unroll
-                    for (int g = 0; g < 16; ++g) tt::st8(drow + g * 8, tt::pack8(v + g * 8));
+                        for (int g = 0; g < 16; ++g) tt::st8(drow + g * 8, tt::pack8(v + g * 8));
+                    }
+                } else {
+                    // One thread per row stores 16 bytes per instruction: 32 scattered 16-byte writes, which reach a peer GPU
+                    // as 32 small NVLink packets.  Instead the warp's 32 x 128 block goes through shared memory (16-byte
+                    // chunks XOR-swizzled by row, so neither side has more than 2-way bank conflicts) and every store
+                    // instruction then covers two whole 256-byte rows.
+                    const uint32_t sst = epi_stage + (uint32_t)(warp - 2) * 8192u;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) {
+                        const tt::bf16x8 pk = tt::pack8(v + g * 8);
+                        const uint4 u = *reinterpret_cast<const uint4*>(&pk);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sst + lane * 256u + (uint32_t)((g ^ (lane & 15)) << 4)),
+                                     "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                                     : "memory");
+                    }
+                    __syncwarp();
+                    const unsigned long long dptr = (unsigned long long)drow;       // 0 for rows that are not stored
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        const int r = 2 * t + (lane >> 4), j = lane & 15;
+                        uint4 u;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                                     : "r"(sst + r * 256u + (uint32_t)((j ^ (r & 15)) << 4))
+                                     : "memory");
+                        const unsigned long long dst = __shfl_sync(0xffffffffu, dptr, r);
+                        if (dst != 0ull) *reinterpret_cast<uint4*>(dst + (unsigned long long)j * 16ull) = u;
+                    }
+                    __syncwarp();       // the staging block is reused for the next head of this tile
                 }
               }
             } else {
@@ -452,15 +488,17 @@ template <int BN, bool A_MN, bool B_MN, int EPI, bool STAGE = false>
 int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t st) {
     using C = Cfg<BN>;
     auto kern = gemm_kernel<BN, A_MN, B_MN, EPI, STAGE>;
+    constexpr int kEpiStage = EPI == 5 ? 4 * 8192 : 0;          // staging for the coalesced fused-QKV stores
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes + kEpiStage);
         if (e != cudaSuccess) return tt_record_cuda(e);
         configured = true;
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, STAGE ? kThreads + 128 : kThreads, C::kSmemBytes, st>>>(tmA, tmB, p);
+    const int smem = C::kSmemBytes + ((EPI == 5 && p.coalesce) ? kEpiStage : 0);
+    kern<<<grid, STAGE ? kThreads + 128 : kThreads, smem, st>>>(tmA, tmB, p);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }
@@ -808,6 +846,9 @@ extern "C" int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias,
     p.s_out = s_out;
     p.out_off = out_off;
     p.only_local = only_local;
+    // TELETRON_B200_QKV_COALESCE=1: coalesced (shared-memory staged) stores of the fused epilogue; off by default
+    static const int coalesce = [] { const char* v = getenv("TELETRON_B200_QKV_COALESCE"); return (v != nullptr && v[0] == '1') ? 1 : 0; }();
+    p.coalesce = coalesce;
     for (int r = 0; r < n; ++r) {
         p.peer_q[r] = (__nv_bfloat16*)q_ptrs[r];
         p.peer_k[r] = (__nv_bfloat16*)k_ptrs[r];
