@@ -72,7 +72,7 @@ struct GemmParams {
     const float* sin_t;
     float eps;
     int rope_len, heads_per_rank, s_in, s_out, out_off, only_local;
-    int coalesce;           // EPI 5: stage each warp's 32 x 128 block in shared memory and store 512 contiguous bytes per instruction
+    int coalesce;           // pushed tiles: stage each warp's 32 x 128 block in shared memory, store whole 256-byte rows
     __nv_bfloat16* peer_q[TT_MAX_PEERS];
     __nv_bfloat16* peer_k[TT_MAX_PEERS];
     __nv_bfloat16* peer_v[TT_MAX_PEERS];
@@ -90,7 +90,7 @@ struct Cfg {
 
 template <int EPI>
 __device__ __forceinline__ float epi_apply(float acc, float b, float u) {
-    if (EPI == 0) return acc + b;
+    if (EPI == 0 || EPI == 6) return acc + b;
     if (EPI == 1) return tt::gelu_erf(acc + b);
     if (EPI == 2) return tt::gelu_tanh(acc + b);
     if (EPI == 3) return acc * tt::gelu_erf_grad(u);
@@ -121,7 +121,7 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
     auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::kStages + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::kStages + 2 + b); };
-    const uint32_t epi_stage = bar_base + 256u;      // EPI 5 with coalesced stores: 4 warps x 8 KB (only when launched with room for it)
+    const uint32_t epi_stage = bar_base + 256u;      // coalesced peer stores: 4 warps x 8 KB (only when launched with room for it)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -301,6 +301,35 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quad = warp & 3;
+        // Coalesced store of this warp's 32 rows x 128 columns (lane = row, v = the row's values, dst = where the row's 128
+        // columns go, nullptr for rows that are not stored; only the first `ncols` columns are written).  The block goes
+        // through shared memory, 16-byte chunks XOR-swizzled by row so that neither side has more than 2-way bank
+        // conflicts, and every store instruction then covers two whole 256-byte rows.
+        auto store_block_coalesced = [&](const float* v, __nv_bfloat16* dst_row, int ncols) {
+            const uint32_t sst = epi_stage + (uint32_t)(warp - 2) * 8192u;
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+                const tt::bf16x8 pk = tt::pack8(v + g * 8);
+                const uint4 u = *reinterpret_cast<const uint4*>(&pk);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sst + lane * 256u + (uint32_t)((g ^ (lane & 15)) << 4)),
+                             "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                             : "memory");
+            }
+            __syncwarp();
+            const unsigned long long dptr = (unsigned long long)dst_row;
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                const int r = 2 * t + (lane >> 4), j = lane & 15;
+                uint4 u;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                             : "r"(sst + r * 256u + (uint32_t)((j ^ (r & 15)) << 4))
+                             : "memory");
+                const unsigned long long dst = __shfl_sync(0xffffffffu, dptr, r);
+                if (dst != 0ull && j * 8 + 8 <= ncols) *reinterpret_cast<uint4*>(dst + (unsigned long long)j * 16ull) = u;
+            }
+            __syncwarp();       // the staging block is reused by the next call
+        };
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             int seg, m0, n0;
@@ -392,29 +421,7 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                     // as 32 small NVLink packets.  Instead the warp's 32 x 128 block goes through shared memory (16-byte
                     // chunks XOR-swizzled by row, so neither side has more than 2-way bank conflicts) and every store
                     // instruction then covers two whole 256-byte rows.
-                    const uint32_t sst = epi_stage + (uint32_t)(warp - 2) * 8192u;
-#pragma unroll
-                    for (int g = 0; g < 16; ++g) {
-                        const tt::bf16x8 pk = tt::pack8(v + g * 8);
-                        const uint4 u = *reinterpret_cast<const uint4*>(&pk);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sst + lane * 256u + (uint32_t)((g ^ (lane & 15)) << 4)),
-                                     "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
-                                     : "memory");
-                    }
-                    __syncwarp();
-                    const unsigned long long dptr = (unsigned long long)drow;       // 0 for rows that are not stored
-#pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        const int r = 2 * t + (lane >> 4), j = lane & 15;
-                        uint4 u;
-                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
-                                     : "r"(sst + r * 256u + (uint32_t)((j ^ (r & 15)) << 4))
-                                     : "memory");
-                        const unsigned long long dst = __shfl_sync(0xffffffffu, dptr, r);
-                        if (dst != 0ull) *reinterpret_cast<uint4*>(dst + (unsigned long long)j * 16ull) = u;
-                    }
-                    __syncwarp();       // the staging block is reused for the next head of this tile
+                    store_block_coalesced(v, drow, 128);
                 }
               }
             } else {
@@ -436,6 +443,43 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                     crow = p.peer_out[seg] + ((long)p.my_rank * p.seg_rows + lrow) * p.out_ld;
                 }
                 __nv_bfloat16* arow = (EPI != 0) ? p.aux + (long)row * p.ldc : nullptr;
+                if (EPI == 6) {
+                    // tiles pushed to a peer (column blocks of a dgrad, row blocks of a reduce-scatter): 128 columns at a time
+                    // through the staged store, for the same reason as in the fused QKV epilogue
+#pragma unroll 1
+                    for (int c4 = 0; c4 < BN / 128; ++c4) {
+                        const int colb = n0 + c4 * 128;
+                        if (colb >= p.N) break;
+                        float v[128];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(tacc + c4 * 128 + c * 32, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                float bv[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+                                const int col = colb + c * 32 + g * 8;
+                                if (p.bias != nullptr && col + 8 <= p.N) tt::unpack8(tt::ld8(p.bias + col), bv);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[c * 32 + g * 8 + j] = __uint_as_float(r[g * 8 + j]) + bv[j];
+                            }
+                        }
+                        __nv_bfloat16* d = nullptr;
+                        if (row_ok) {
+                            if (p.store_mode == 1) {
+                                const int dest = colb / p.out_span;        // out_span is a multiple of 128: one owner per group
+                                d = dest < p.n_dest ? p.peer_out[dest] + (long)(p.out_row_off + row) * p.out_ld + (colb - dest * p.out_span)
+                                                    : p.C + (long)row * p.ldc + (colb - p.n_dest * p.out_span);
+                            } else {
+                                d = crow + colb;
+                            }
+                        }
+                        store_block_coalesced(v, d, min(128, p.N - colb));
+                    }
+                } else
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
@@ -488,16 +532,17 @@ template <int BN, bool A_MN, bool B_MN, int EPI, bool STAGE = false>
 int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, int sms, cudaStream_t st) {
     using C = Cfg<BN>;
     auto kern = gemm_kernel<BN, A_MN, B_MN, EPI, STAGE>;
-    constexpr int kEpiStage = EPI == 5 ? 4 * 8192 : 0;          // staging for the coalesced fused-QKV stores
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes + kEpiStage);
+    // staging for the coalesced peer stores (4 epilogue warps x 8 KB), only when that variant is selected
+    const bool staged_stores = EPI == 6 || (EPI == 5 && p.coalesce);
+    const int smem = C::kSmemBytes + (staged_stores ? 4 * 8192 : 0);
+    static int configured = 0;
+    if (configured < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return tt_record_cuda(e);
-        configured = true;
+        configured = smem;
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
-    const int smem = C::kSmemBytes + ((EPI == 5 && p.coalesce) ? kEpiStage : 0);
     kern<<<grid, STAGE ? kThreads + 128 : kThreads, smem, st>>>(tmA, tmB, p);
     TT_CHECK_LAUNCH();
     return TT_OK;
@@ -511,8 +556,10 @@ int dispatch(bool a_mn, bool b_mn, int epi, const TmapArray& tmA, const CUtensor
         if (epi == 1) return launch<BN, false, false, 1>(tmA, tmB, p, sms, st);
         if (epi == 2) return launch<BN, false, false, 2>(tmA, tmB, p, sms, st);
         if (epi == 5) return launch<BN, false, false, 5>(tmA, tmB, p, sms, st);
+        if (epi == 6) return launch<BN, false, false, 6>(tmA, tmB, p, sms, st);
     } else if (!a_mn && b_mn) {
         if (epi == 0) return launch<BN, false, true, 0>(tmA, tmB, p, sms, st);
+        if (epi == 6) return launch<BN, false, true, 6>(tmA, tmB, p, sms, st);
         if (epi == 3) return launch<BN, false, true, 3>(tmA, tmB, p, sms, st);
         if (epi == 4) return launch<BN, false, true, 4>(tmA, tmB, p, sms, st);
     } else if (a_mn && b_mn) {
@@ -604,6 +651,16 @@ void default_params(GemmParams& p) {
     p.n_seg = 1;
 }
 
+// TELETRON_B200_COALESCED_PEER_STORES=1: epilogues that push tiles to a peer stage them in shared memory and store whole
+// 256-byte rows per instruction; off by default
+int coalesced_peer_stores() {
+    static const int on = [] {
+        const char* v = getenv("TELETRON_B200_COALESCED_PEER_STORES");
+        return (v != nullptr && v[0] == '1') ? 1 : 0;
+    }();
+    return on;
+}
+
 int pick_bn(int M, int N, int sms, bool force128) {
     // 128 x 256 tiles unless they would leave most SMs idle or N is not a multiple of 256 but is of 128
     const long tiles256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
@@ -616,7 +673,8 @@ int pick_bn(int M, int N, int sms, bool force128) {
 //   a_mn == 0: a is A[M, K] with row pitch lda;   a_mn == 1: a is A^T stored [K, M] with row pitch lda
 //   b_mn == 0: b is B[N, K] with row pitch ldb;   b_mn == 1: b is B stored [K, N] with row pitch ldb
 //   epi: 0 bias (optional); 1 / 2 bias + GELU erf / tanh, pre-activation written to aux;
-//        3 / 4 multiply by GELU'(aux) erf / tanh.
+//        3 / 4 multiply by GELU'(aux) erf / tanh.  (Internal codes: 5 = the fused QKV epilogue of tt_qkv_gemm_fused,
+//        6 = bias with staged, coalesced stores for tiles pushed to a peer by tt_gemm_comm_bf16.)
 //   status: device int, set to TT_ERR_TIMEOUT if a bounded wait inside the kernel gave up.
 extern "C" int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K,
                             long lda, long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream) {
@@ -723,6 +781,7 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
     p.seg_rot = segmented ? my_rank : 0;       // own rows first: they need no peer traffic
     p.my_rank = my_rank;
     p.store_mode = store_mode;
+    p.coalesce = (store_mode != 0 && bias == nullptr) ? coalesced_peer_stores() : 0;
     p.out_span = out_span;
     p.out_row_off = out_row_off;
     p.out_ld = out_ld;
@@ -739,8 +798,9 @@ extern "C" int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_
         return BN == 128 ? launch<128, false, false, 0, true>(tmA, tmB, p, sms, st)
                          : launch<256, false, false, 0, true>(tmA, tmB, p, sms, st);
     }
-    return BN == 128 ? dispatch<128>(false, b_mn != 0, 0, tmA, tmB, p, sms, st)
-                     : dispatch<256>(false, b_mn != 0, 0, tmA, tmB, p, sms, st);
+    const int epi = p.coalesce ? 6 : 0;          // 6 = bias epilogue with staged, coalesced peer stores
+    return BN == 128 ? dispatch<128>(false, b_mn != 0, epi, tmA, tmB, p, sms, st)
+                     : dispatch<256>(false, b_mn != 0, epi, tmA, tmB, p, sms, st);
 }
 
 // Tensor-parallel all-gather -> GEMM with the epilogues of the plain GEMM: C[n * seg_rows, N] = epi(gather_r(A_r) op(B) + bias).
@@ -846,9 +906,7 @@ extern "C" int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias,
     p.s_out = s_out;
     p.out_off = out_off;
     p.only_local = only_local;
-    // TELETRON_B200_QKV_COALESCE=1: coalesced (shared-memory staged) stores of the fused epilogue; off by default
-    static const int coalesce = [] { const char* v = getenv("TELETRON_B200_QKV_COALESCE"); return (v != nullptr && v[0] == '1') ? 1 : 0; }();
-    p.coalesce = coalesce;
+    p.coalesce = coalesced_peer_stores();
     for (int r = 0; r < n; ++r) {
         p.peer_q[r] = (__nv_bfloat16*)q_ptrs[r];
         p.peer_k[r] = (__nv_bfloat16*)k_ptrs[r];
