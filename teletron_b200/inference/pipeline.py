@@ -133,7 +133,9 @@ class HunyuanVideoPipeline:
         cond = mask_lat = first_lat = last_lat = None
         if ref_images is not None:
             ref = ref_images.to(dev, dtype)
-            enc = lambda img: self.vae.encode(img.unsqueeze(0).permute(0, 2, 1, 3, 4), generator=None) * self.vae_scaling_factor  # noqa: E731
+            # the posterior sample of a reference frame is drawn from the call's generator (the reference draws it from the
+            # global RNG, examples/hunyuanvideo/pipelines.py:824-826, so a fixed seed did not fix the video)
+            enc = lambda img: self.vae.encode(img.unsqueeze(0).permute(0, 2, 1, 3, 4), generator=generator) * self.vae_scaling_factor  # noqa: E731
             if model_type == "i2v":
                 first = enc(ref[:1]).to(dtype)
                 cond = F.pad(first, (0, 0, 0, 0, 0, f - first.shape[2])).expand(B, -1, -1, -1, -1)
