@@ -47,7 +47,8 @@ def main():
     p.add_argument("--cfg_zero_star", action="store_true")
     a = p.parse_args()
     pipe = HunyuanVideoPipeline.from_pretrained(a.base_model_path, transformer_model_path=a.transformer_model_path,
-                                                torch_dtype=torch.bfloat16, device=torch.device(a.device))
+                                                torch_dtype=torch.bfloat16, device=torch.device(a.device),
+                                                in_channels=33 if a.model_type == "i2v" else 16)
     pipe.vae.enable_tiling()
     ref = prepare_reference_images(a.width, a.height, a.num_frames, a.ref_frame) if a.model_type != "t2v" else None
     out = pipe(prompt=a.prompt, height=a.height, width=a.width, num_frames=a.num_frames,

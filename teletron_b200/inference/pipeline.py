@@ -75,11 +75,18 @@ class HunyuanVideoPipeline:
         from ..models.hunyuanvideo import HunyuanVideoTransformer3DModel, hunyuan_13b
         from ..models.text_encoders import ClipTextEncoder, LlamaTextEncoder
         from ..models.vae import AutoencoderKLHunyuanVideo
-        cfg = cfg or hunyuan_13b()
-        tr = HunyuanVideoTransformer3DModel(cfg, tp=1, device=device, dtype=torch_dtype).eval()
+        sd = None
         if transformer_model_path:
             from ..convert_ckpt.hunyuan.convert_hunyuanvideo import load_tel_checkpoint, merge_shards
-            sd = merge_shards(load_tel_checkpoint(transformer_model_path), cfg.hidden_size, cfg.mlp_hidden)
+            base = cfg or hunyuan_13b()
+            sd = merge_shards(load_tel_checkpoint(transformer_model_path), base.hidden_size, base.mlp_hidden)
+        if cfg is None:
+            # 33 input channels for first-frame-conditioned (i2v) weights, 16 otherwise: read from the checkpoint when there
+            # is one, else from the ``in_channels`` keyword
+            w = None if sd is None else sd.get("x_embedder.proj.weight")
+            cfg = hunyuan_13b(in_channels=int(w.shape[1]) if w is not None else int(kw.get("in_channels", 16)))
+        tr = HunyuanVideoTransformer3DModel(cfg, tp=1, device=device, dtype=torch_dtype).eval()
+        if sd is not None:
             tr.load_state_dict(sd, strict=False)
         vae = AutoencoderKLHunyuanVideo().to(device, torch_dtype).eval()
         sub = lambda n: (os.path.join(base_model_path, n) if base_model_path and os.path.isdir(os.path.join(base_model_path, n)) else None)  # noqa: E731
