@@ -267,3 +267,16 @@ def test_heartbeat_reports_departed_and_silent_ranks():
     assert hb[0].dead_ranks() == [1, 2]        # rank 2 stopped beating
     hb[2].beat()
     assert hb[0].dead_ranks() == [1]
+
+
+def test_max_frames_proposal_stays_under_the_limit():
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("max_frames", os.path.join(os.path.dirname(__file__), "..", "benchmarks", "max_frames.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    # 1 GB per latent frame on top of 75 GB fixed: 90 latent frames (357 frames) fit under 165 GB, 91 do not
+    f = m.propose(33, 84.0, 65, 92.0, 165.0)
+    assert f == 357 and m.latent_frames(f) == 90
+    with pytest.raises(ValueError):
+        m.propose(33, 84.0, 35, 84.0, 165.0)
