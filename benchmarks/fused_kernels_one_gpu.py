@@ -69,7 +69,7 @@ def main():
     x = rnd(s, H)
     w, b = rnd(heads * 384, H, scale=0.02), rnd(heads * 384, scale=0.02)
     qw, kw = torch.ones(128, device=dev, dtype=BF16), torch.ones(128, device=dev, dtype=BF16)
-    cos, sin = torch.rand(s, 128, device=dev), torch.rand(s, 128, device=dev)
+    cos, sin = torch.rand(s, 128, device=dev, generator=g), torch.rand(s, 128, device=dev, generator=g)
     S_tot = n * s
     qb, kb, vb = ([torch.empty(heads // n, S_tot, 128, device=dev, dtype=BF16) for _ in range(n)] for _ in range(3))
     aux = torch.empty(s, heads * 384, device=dev, dtype=BF16)
@@ -79,7 +79,8 @@ def main():
              c_int(n), c_int(me), ptr(aux), c_int(s), c_int(heads), c_int(H), c_int(s), c_int(S_tot), c_int(me * s), c_int(s),
              c_int(0), c_float(1e-6), ptr(st), stream())
     ms = timeit(qkv, a.iters)
-    res["a_qkv_norm_rope_scatter"] = {"ms": ms, "tflops": 2.0 * s * H * heads * 384 / ms / 1e9}
+    res["a_qkv_norm_rope_scatter"] = {"ms": ms, "tflops": 2.0 * s * H * heads * 384 / ms / 1e9,
+                                      "checksum": sum(float(t[:, me * s:(me + 1) * s].float().abs().sum()) for t in qb + kb + vb)}
 
     # (c) all-gather -> GEMM: n row blocks of [s / n, H] (all local), column-parallel weight [ffn / n, H]
     rows = s // n // 8 * 8
@@ -108,7 +109,8 @@ def main():
              ptr(w2), c_int(0), c_long(a.ffn // n), None, c_long(0), None, c_int(n * rows), c_int(H), c_int(a.ffn // n),
              c_int(rows), c_int(me), c_int(2), table(zones), c_int(0), c_int(0), c_long(H), None, None, c_int(0), ptr(st), stream())
     ms = timeit(rs, a.iters)
-    res["c_gemm_reduce_scatter_push"] = {"ms": ms, "tflops": 2.0 * n * rows * H * (a.ffn // n) / ms / 1e9}
+    res["c_gemm_reduce_scatter_push"] = {"ms": ms, "tflops": 2.0 * n * rows * H * (a.ffn // n) / ms / 1e9,
+                                         "checksum": sum(float(z[me].float().abs().sum()) for z in zones)}
 
     # (d) gradient reduce-scatter: this rank's shard of n "peer" gradient buffers
     count = 64 << 20
