@@ -94,6 +94,48 @@ class FragmentSampleFrames:
         return np.mod(idx, max(total_frames, 1)).astype(np.int64) + start_index
 
 
+class UnifiedFrameSampler:
+    """``fragments_t`` temporal cells, ``fsize_t`` frames (``frame_interval`` apart) from a random offset inside each
+    cell, optionally dropping a share of the cells; indices wrap around the clip (``koala_dataset.py:45-94``)."""
+
+    def __init__(self, fsize_t: int, fragments_t: int, frame_interval: int = 1, num_clips: int = 1, drop_rate: float = 0.0):
+        self.fsize_t, self.fragments_t = fsize_t, fragments_t
+        self.size_t = fragments_t * fsize_t
+        self.frame_interval, self.num_clips, self.drop_rate = frame_interval, num_clips, drop_rate
+
+    def get_frame_indices(self, num_frames: int, train: bool = False) -> np.ndarray:
+        cell = num_frames // self.fragments_t
+        starts = np.arange(self.fragments_t, dtype=np.int64) * cell
+        span = self.fsize_t * self.frame_interval
+        offs = np.random.randint(0, cell - span, size=self.fragments_t) if cell > span else np.zeros(self.fragments_t, dtype=np.int64)
+        ranges = np.arange(self.fsize_t)[None, :] * self.frame_interval + offs[:, None] + starts[:, None]
+        dropped = set(random.sample(range(self.fragments_t), int(self.fragments_t * self.drop_rate)))
+        return np.concatenate([r for i, r in enumerate(ranges) if i not in dropped])
+
+    def __call__(self, total_frames: int, train: bool = False, start_index: int = 0) -> np.ndarray:
+        inds = np.concatenate([self.get_frame_indices(total_frames, train) for _ in range(self.num_clips)])
+        return np.mod(inds + start_index, total_frames).astype(np.int32)
+
+
+class SimpleFrameSampler:
+    """Evenly spread frames including the first and the last one (one frame: the middle; two: first and middle),
+    ``koala_dataset.py:97-119``."""
+
+    def __init__(self, fsize_t: int):
+        self.fsize_t = fsize_t
+
+    def __call__(self, total_frames: int, train: bool = False, start_index: int = 0) -> np.ndarray:
+        n = self.fsize_t
+        if n == 1:
+            inds = [total_frames // 2]
+        elif n == 2:
+            inds = [0, total_frames // 2]
+        else:
+            step = total_frames // (n - 1)
+            inds = [0] + [step * (i + 1) for i in range(n - 2)] + [total_frames - 1]
+        return np.asarray(inds, dtype=np.int32)
+
+
 def get_spatial_fragments(video: torch.Tensor, fragments_h: int = 1, fragments_w: int = 1, fsize_h: int = 720,
                           fsize_w: int = 1280, aligned: int = 1, random: bool = False, **_unused) -> torch.Tensor:
     """Grid mini-patch sampling on ``[C, T, H, W]``: one ``fsize`` patch from each cell of a
@@ -136,14 +178,90 @@ def get_resized_video(video: torch.Tensor, size_h: int = 224, size_w: int = 224,
     return F.interpolate(v, size=(size_h, size_w), mode="bilinear", align_corners=False).permute(1, 0, 2, 3)
 
 
+def _random_square_crop(video: torch.Tensor) -> torch.Tensor:
+    """Random crop of ``[..., H, W]`` to a square of the short edge (training-time augmentation of the aspect-ratio
+    preserving sample types; the reference's version indexes the wrong axis for wide clips, ``koala_dataset.py:266-268``)."""
+    H, W = video.shape[-2:]
+    e = min(H, W)
+    if H > e:
+        o = random.randrange(H - e)
+        return video[..., o:o + e, :]
+    if W > e:
+        o = random.randrange(W - e)
+        return video[..., :, o:o + e]
+    return video
+
+
+def get_arp_resized_video(video: torch.Tensor, short_edge: int = 224, train: bool = False, **_unused) -> torch.Tensor:
+    """Resize ``[C, T, H, W]`` so that the short edge becomes ``short_edge``, keeping the aspect ratio (training: after a
+    random square crop)."""
+    if train:
+        video = _random_square_crop(video)
+    scale = short_edge / min(video.shape[-2:])
+    out = F.interpolate(video.permute(1, 0, 2, 3).float(), scale_factor=scale, mode="bilinear", align_corners=False)
+    return out.permute(1, 0, 2, 3).to(video.dtype) if video.dtype.is_floating_point else out.permute(1, 0, 2, 3)
+
+
+def get_arp_fragment_video(video: torch.Tensor, short_fragments: int = 7, fsize: int = 32, train: bool = False,
+                           **kwargs) -> torch.Tensor:
+    """Grid fragments with ``short_fragments`` cells along the short edge and proportionally more along the long one."""
+    if train:
+        video = _random_square_crop(video)
+    H, W = video.shape[-2:]
+    if H > W:
+        fh, fw = int(short_fragments * H / W), short_fragments
+    else:
+        fh, fw = short_fragments, int(short_fragments * W / H)
+    kwargs.pop("fragments_h", None)
+    kwargs.pop("fragments_w", None)
+    return get_spatial_fragments(video, fragments_h=fh, fragments_w=fw, fsize_h=fsize, fsize_w=fsize, **kwargs)
+
+
+def get_cropped_video(video: torch.Tensor, size_h: int = 224, size_w: int = 224, **kwargs) -> torch.Tensor:
+    """One ``size_h x size_w`` window (centre, or random with ``random=True``): a 1 x 1 fragment grid."""
+    for k in ("fragments_h", "fragments_w", "fsize_h", "fsize_w"):
+        kwargs.pop(k, None)
+    return get_spatial_fragments(video, fragments_h=1, fragments_w=1, fsize_h=size_h, fsize_w=size_w, **kwargs)
+
+
 def get_single_sample(video: torch.Tensor, sample_type: str, random: bool = False, **kwargs) -> torch.Tensor:
-    if sample_type.startswith("resize"):
+    """Dispatch on the sample-type prefix (``koala_dataset.py:315-337``).  ``arp_*`` must be tested before their
+    un-prefixed namesakes; the reference tests ``resize`` first, so its ``arp_resize`` branch is dead."""
+    if sample_type.startswith("arp_resize"):
+        return get_arp_resized_video(video, **kwargs)
+    if sample_type.startswith("arp_fragments"):
+        return get_arp_fragment_video(video, random=random, **kwargs)
+    if sample_type.startswith(("resize", "image", "semantic")):
         return get_resized_video(video, **kwargs)
     if sample_type.startswith("fragments"):
         return get_spatial_fragments(video, random=random, **kwargs)
+    if sample_type.startswith("crop"):
+        return get_cropped_video(video, random=random, **kwargs)
     if sample_type.startswith("original"):
         return video
     raise ValueError(f"unknown sample type {sample_type}")
+
+
+def get_spatial_samples(video: torch.Tensor, random_crop: int = 0, sample_types: Optional[Dict[str, dict]] = None) -> Dict[str, torch.Tensor]:
+    """All spatial views of one decoded clip ``[C, T, H, W]``.  ``random_crop`` 1: random window of 80-100 % keeping the
+    aspect ratio, then up-scaled by 1.0-1.3; 2: random near-square window of 80-100 % of the short edge
+    (``koala_dataset.py:339-371``, whose mode 1 references an undefined name)."""
+    H, W = video.shape[-2:]
+    if random_crop == 1:
+        r = random.random() * 0.2 + 0.8
+        nh, nw = int(r * H), int(r * W)
+        oh, ow = random.randrange(max(H - nh, 1)), random.randrange(max(W - nw, 1))
+        video = video[..., oh:oh + nh, ow:ow + nw]
+        up = random.random() * 0.3 + 1.0
+        scaled = F.interpolate(video.permute(1, 0, 2, 3).float(), scale_factor=up, mode="bilinear", align_corners=False)
+        video = scaled.permute(1, 0, 2, 3).to(video.dtype) if video.dtype.is_floating_point else scaled.permute(1, 0, 2, 3)
+    elif random_crop == 2:
+        r = random.random() * 0.2 + 0.8
+        n = int(r * min(H, W))
+        oh, ow = random.randrange(max(H - n, 1)), random.randrange(max(W - n, 1))
+        video = video[..., oh:oh + n, ow:ow + n]
+    sample_types = sample_types if sample_types is not None else {"resize": {}, "fragments": {}}
+    return {name: get_single_sample(video, name, **(opt or {})) for name, opt in sample_types.items()}
 
 
 def read_video(path: str, frame_indices: Optional[np.ndarray] = None) -> torch.Tensor:
@@ -247,6 +365,41 @@ class KoalaDataset(Dataset):
         return {"images": frames, "first_ref_image": frames[0], "prompt": info["prompt"],
                 "prompt_embeds": info["prompt_embeds"], "clip_text_embed": info["clip_text_embed"],
                 "latents": info["latents"]}
+
+
+@DATASETS.register_module()
+class SimpleDataset(Dataset):
+    """Labelled clips with one sample type (``koala_dataset.py:549-604``): ``opt`` carries ``anno_file`` (a path whose
+    lines are ``filename,_,_,label``, or a ready list of ``{"filename", "label"}``), ``data_prefix``, ``sample_type``,
+    ``sampling_args``, ``phase``, ``clip_len``, ``frame_interval`` and ``num_clips``."""
+
+    def __init__(self, opt: dict):
+        self.opt = opt
+        self.sample_type, self.phase = opt["sample_type"], opt["phase"]
+        self.sampler = SampleFrames(opt["clip_len"], opt["frame_interval"], opt["num_clips"])
+        ann = opt["anno_file"]
+        if isinstance(ann, list):
+            self.video_infos = list(ann)
+        else:
+            self.video_infos = []
+            with open(ann) as f:
+                for line in f:
+                    if not line.strip():
+                        continue
+                    name, _, _, label = line.strip().split(",")
+                    self.video_infos.append({"filename": os.path.join(opt["data_prefix"], name), "label": float(label)})
+
+    def __len__(self):
+        return len(self.video_infos)
+
+    def __getitem__(self, index: int):
+        info = self.video_infos[index]
+        inds = self.sampler(video_num_frames(info["filename"]), self.phase == "train")
+        video = read_video(info["filename"], inds).permute(3, 0, 1, 2).float()            # [C, T, H, W]
+        video = get_single_sample(video, self.sample_type, **self.opt.get("sampling_args", {}))
+        video = ((video.permute(1, 2, 3, 0) - IMAGENET_MEAN) / IMAGENET_STD).permute(3, 0, 1, 2)
+        return {"video": video, "num_clips": self.opt["num_clips"], "frame_inds": inds, "gt_label": info["label"],
+                "name": os.path.basename(info["filename"])}
 
 
 def seed_worker(worker_id: int) -> None:

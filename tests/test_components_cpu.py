@@ -199,6 +199,43 @@ def test_koala_dataset_reads_tensor_clips(tmp_path):
     assert item["prompt"] == "a prompt" and item["latents"].shape == (2, 3, 2, 2)
 
 
+def test_koala_samplers_and_spatial_sample_types(tmp_path):
+    import numpy as np
+    from teletron_b200.data import koala_dataset as K
+    np.random.seed(0)
+    u = K.UnifiedFrameSampler(fsize_t=4, fragments_t=3, frame_interval=2)
+    inds = u(60)
+    assert inds.shape == (12,) and inds.min() >= 0 and inds.max() < 60
+    for c in range(3):                                   # four frames, two apart, inside each third of the clip
+        cell = inds[4 * c:4 * c + 4]
+        assert (np.diff(cell) == 2).all() and 20 * c <= cell[0] and cell[-1] < 20 * (c + 1)
+    assert len(K.UnifiedFrameSampler(4, 4, drop_rate=0.5)(64)) == 8
+    s = K.SimpleFrameSampler
+    assert s(1)(31).tolist() == [15] and s(2)(31).tolist() == [0, 15] and s(4)(31).tolist() == [0, 10, 20, 30]
+    video = torch.arange(3 * 2 * 48 * 64, dtype=torch.float32).reshape(3, 2, 48, 64)     # wide clip
+    assert K.get_arp_resized_video(video, short_edge=24).shape == (3, 2, 24, 32)          # aspect ratio kept
+    assert K.get_arp_resized_video(video, short_edge=24, train=True).shape == (3, 2, 24, 24)   # square crop first
+    assert K.get_arp_fragment_video(video, short_fragments=3, fsize=8).shape == (3, 2, 24, 32)  # 3 x 4 cells of 8
+    crop = K.get_cropped_video(video, size_h=16, size_w=16)
+    assert crop.shape == (3, 2, 16, 16) and torch.equal(crop, video[:, :, 16:32, 24:40])  # centre window
+    assert K.get_single_sample(video, "arp_resize_sem", short_edge=12).shape == (3, 2, 12, 16)
+    assert K.get_single_sample(video, "semantic", size_h=8, size_w=8).shape == (3, 2, 8, 8)
+    both = K.get_spatial_samples(video, random_crop=2, sample_types={"resize": {"size_h": 8, "size_w": 8},
+                                                                      "crop": {"size_h": 8, "size_w": 8}})
+    assert both["resize"].shape == both["crop"].shape == (3, 2, 8, 8)
+    assert K.get_spatial_samples(video, random_crop=1, sample_types={"original": {}})["original"].shape[0] == 3
+    with pytest.raises(ValueError):
+        K.get_single_sample(video, "nonsense")
+    # labelled-clip dataset
+    torch.save(torch.randint(0, 255, (12, 20, 24, 3), dtype=torch.uint8), tmp_path / "c.pt")
+    (tmp_path / "labels.txt").write_text("c.pt,0,0,3.5\n")
+    ds = K.SimpleDataset({"anno_file": str(tmp_path / "labels.txt"), "data_prefix": str(tmp_path), "sample_type": "resize",
+                          "sampling_args": {"size_h": 16, "size_w": 16}, "phase": "test", "clip_len": 4, "frame_interval": 2,
+                          "num_clips": 1})
+    item = ds[0]
+    assert len(ds) == 1 and item["video"].shape == (3, 4, 16, 16) and item["gt_label"] == 3.5 and item["name"] == "c.pt"
+
+
 # ---------------------------------------------------------------- models around the DiT
 def test_vae_shapes_tiling_and_roundtrip_geometry():
     from teletron_b200.models.vae import AutoencoderKLHunyuanVideo
