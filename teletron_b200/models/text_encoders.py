@@ -116,36 +116,120 @@ class ClipTextEncoder:
         return out.pooler_output if pooled else out.last_hidden_state
 
 
-class PromptEncoder:
-    """Lazy-loading front end with the reference's modes.  ``mode`` in ``{"llama", "clip_text", "clip_text_proj"}``."""
+def t5_config(num_layers: int = 24, hidden: int = 4096, heads: int = 64, ffn: int = 10240, vocab: int = 32128):
+    from transformers import T5Config
+    return T5Config(vocab_size=vocab, d_model=hidden, d_kv=hidden // heads, d_ff=ffn, num_layers=num_layers, num_heads=heads,
+                    feed_forward_proj="gated-gelu", is_encoder_decoder=False, use_cache=False)
 
-    def __init__(self, mode: str, model_path: Optional[str] = None, device=None, dtype=None, max_length: Optional[int] = None):
+
+class _HFTextModel:
+    """One Hugging Face text model + tokenizer (a hashing stand-in when no weights are given)."""
+
+    def __init__(self, kind: str, model_path: Optional[str], max_length: int, device, dtype, config=None):
+        import transformers
+        cls = {"clip": transformers.CLIPTextModel, "clip_proj": transformers.CLIPTextModelWithProjection,
+               "t5": transformers.T5EncoderModel}[kind]
+        self.max_length, self.device = max_length, device
+        if model_path:
+            self.model = cls.from_pretrained(model_path, torch_dtype=dtype).to(device).eval()
+            self.tokenizer = transformers.AutoTokenizer.from_pretrained(model_path)
+            self._hash = None
+        else:
+            cfg = config or (t5_config() if kind == "t5" else clip_text_config(max_len=max_length))
+            with torch.device(device or "cpu"):
+                self.model = cls(cfg).to(dtype).eval()
+            self.tokenizer = None
+            self._hash = HashTokenizer(cfg.vocab_size, max_length, pad_id=0)
+        for p in self.model.parameters():
+            p.requires_grad_(False)
+
+    def tokenize(self, prompts, max_length=None):
+        n = max_length or self.max_length
+        if self._hash is not None:
+            return self._hash(prompts, n)
+        t = self.tokenizer(list(prompts), padding="max_length", max_length=n, truncation=True, return_tensors="pt")
+        return t.input_ids, t.attention_mask
+
+    def __call__(self, ids, mask, **kw):
+        return self.model(input_ids=ids.to(self.device), attention_mask=None if mask is None else mask.to(self.device), **kw)
+
+
+class PromptEncoder:
+    """Lazy-loading front end with the reference's five modes (``text_encoder.py:14-50, 125-238``):
+
+    * ``llama``: last hidden state ``[B, L, hidden]``;
+    * ``clip_text``: CLIP text last hidden state ``[B, L, hidden]``;  ``t5``: T5 encoder last hidden state;
+    * ``clip_text_proj``: projected pooled CLIP embedding as ``[B, 1, proj]``;
+    * ``clip_text_and_proj``: two CLIP towers (``text_encoder`` and ``text_encoder_2`` under ``model_path``): the
+      penultimate hidden states concatenated on the feature dim, plus the second tower's projected pooled embedding,
+      returned as ``(embeds, pooled)``.
+
+    Returns ``(embeds, masks)``; ``masks`` is ``None`` unless ``with_attention_mask`` (then the masks are also passed to
+    the encoders, as in the reference).  Without ``model_path`` the models are built from configs with random weights and a
+    hashing tokenizer (``configs``: one config per tower)."""
+
+    MODES = ("llama", "clip_text", "clip_text_proj", "clip_text_and_proj", "t5")
+
+    def __init__(self, mode: str, model_path: Optional[str] = None, device=None, dtype=None, max_length: Optional[int] = None,
+                 configs: Optional[Sequence] = None):
         if dtype is None:
             dtype = torch.float16 if (device is not None and "cuda" in str(device)) else torch.float32
         if isinstance(dtype, str):
             dtype = getattr(torch, dtype)
-        if mode not in ("llama", "clip_text", "clip_text_proj"):
+        if mode not in self.MODES:
             raise ValueError(f"Unsupported mode: {mode}")
         self.mode, self.model_path, self.device, self.dtype = mode, model_path, device, dtype
-        self.max_length = max_length or (256 if mode == "llama" else 77)
-        self.encoder = None
+        self.max_length = max_length or (256 if mode in ("llama", "t5") else 77)
+        self.configs = list(configs) if configs else None
+        self.encoders = None
+
+    def _paths(self):
+        import os
+        if not self.model_path:
+            return [None, None]
+        found = [os.path.join(self.model_path, n) for n in ("text_encoder", "text_encoder_2")
+                 if os.path.exists(os.path.join(self.model_path, n))]
+        return (found or [self.model_path]) + [None]
 
     def load_model(self):
-        if self.encoder is None:
-            cls = LlamaTextEncoder if self.mode == "llama" else ClipTextEncoder
-            self.encoder = cls(self.model_path, self.max_length, self.device, self.dtype)
+        if self.encoders is not None:
+            return
+        paths, cfg = self._paths(), (self.configs or [None, None]) + [None]
+        if self.mode == "llama":
+            self.encoders = [LlamaTextEncoder(paths[0], self.max_length, self.device, self.dtype, config=cfg[0])]
+        elif self.mode == "clip_text_and_proj":
+            self.encoders = [_HFTextModel("clip", paths[0], self.max_length, self.device, self.dtype, cfg[0]),
+                             _HFTextModel("clip_proj", paths[1], self.max_length, self.device, self.dtype, cfg[1])]
+        else:
+            kind = {"clip_text": "clip", "clip_text_proj": "clip_proj", "t5": "t5"}[self.mode]
+            self.encoders = [_HFTextModel(kind, paths[0], self.max_length, self.device, self.dtype, cfg[0])]
 
     @torch.no_grad()
     def __call__(self, prompt, max_length: Optional[int] = None, with_attention_mask: bool = False):
         self.load_model()
         prompts = [prompt] if isinstance(prompt, str) else list(prompt)
-        if max_length:
-            self.encoder.max_length = max_length
         if self.mode == "llama":
-            emb, mask = self.encoder(prompts)
+            enc = self.encoders[0]
+            if max_length:
+                enc.max_length = max_length
+            emb, mask = enc(prompts)
             return emb, (mask if with_attention_mask else None)
-        emb = self.encoder(prompts, pooled=self.mode == "clip_text_proj")
-        return (emb.unsqueeze(1) if self.mode == "clip_text_proj" else emb), None
+        toks = [e.tokenize(prompts, max_length) for e in self.encoders]
+        masks = [m for _, m in toks]
+        use = (lambda i: masks[i]) if with_attention_mask else (lambda i: None)
+        if self.mode == "clip_text_and_proj":
+            hidden, pooled = [], None
+            for i, e in enumerate(self.encoders):
+                out = e(toks[i][0], use(i), output_hidden_states=True)
+                pooled = out[0]                         # of interest: the pooled output of the final tower only
+                hidden.append(out.hidden_states[-2])
+            emb = (torch.cat(hidden, dim=-1), pooled)
+        else:
+            out = self.encoders[0](toks[0][0], use(0))
+            emb = out[0].unsqueeze(1) if self.mode == "clip_text_proj" else out[0]
+        if not with_attention_mask:
+            return emb, None
+        return emb, (masks[0] if len(masks) == 1 else masks)
 
 
 def truncate_prompt(prompt_embeds, prompt_masks):

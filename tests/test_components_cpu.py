@@ -273,6 +273,26 @@ def test_text_encoders_from_config():
     assert p.shape == (10, 64) and m.sum() == 4
 
 
+def test_prompt_encoder_modes():
+    from teletron_b200.models.text_encoders import PromptEncoder, clip_text_config, llama_config, t5_config
+    clip_cfg = clip_text_config(2, 32, 4, 500, 12)
+    prompts = ["a cat", "two dogs run"]
+    emb, mask = PromptEncoder("llama", max_length=10, dtype=torch.float32, configs=[llama_config(2, 64, 4, 2, 128, 1000)])(
+        prompts, with_attention_mask=True)
+    assert emb.shape == (2, 10, 64) and mask.shape == (2, 10)
+    emb, mask = PromptEncoder("clip_text", max_length=12, dtype=torch.float32, configs=[clip_cfg])(prompts)
+    assert emb.shape == (2, 12, 32) and mask is None
+    emb, _ = PromptEncoder("clip_text_proj", max_length=12, dtype=torch.float32, configs=[clip_cfg])(prompts)
+    assert emb.shape == (2, 1, 32)                        # projected pooled embedding with a length-1 token axis
+    (emb, pooled), masks = PromptEncoder("clip_text_and_proj", max_length=12, dtype=torch.float32,
+                                         configs=[clip_cfg, clip_text_config(2, 48, 4, 500, 12)])(prompts, with_attention_mask=True)
+    assert emb.shape == (2, 12, 32 + 48) and pooled.shape == (2, 48) and len(masks) == 2   # penultimate states of both towers
+    emb, _ = PromptEncoder("t5", max_length=9, dtype=torch.float32, configs=[t5_config(2, 32, 4, 64, 300)])(prompts[0])
+    assert emb.shape == (1, 9, 32)
+    with pytest.raises(ValueError):
+        PromptEncoder("bert")
+
+
 # ---------------------------------------------------------------- failure detection (host side only)
 def test_step_watchdog_fires_without_heartbeat():
     from teletron_b200.training.watchdog import StepWatchdog
