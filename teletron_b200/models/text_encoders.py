@@ -20,8 +20,9 @@ import torch
 class HashTokenizer:
     """Deterministic word -> id tokenizer with BOS / padding, used when no tokenizer files are available."""
 
-    def __init__(self, vocab_size: int, max_length: int, bos_id: int = 1, pad_id: int = 0):
+    def __init__(self, vocab_size: int, max_length: int, bos_id: int = 1, pad_id: int = 0, eos_id: Optional[int] = None):
         self.vocab_size, self.max_length, self.bos_id, self.pad_id = vocab_size, max_length, bos_id, pad_id
+        self.eos_id = eos_id            # appended to every prompt when set (CLIP pools at its end-of-text token)
 
     def __call__(self, prompts: Sequence[str], max_length: Optional[int] = None):
         L = max_length or self.max_length
@@ -30,7 +31,7 @@ class HashTokenizer:
         for i, p in enumerate(prompts):
             toks = [self.bos_id] + [2 + int.from_bytes(hashlib.md5(w.encode()).digest()[:4], "little") % (self.vocab_size - 2)
                                     for w in p.split()]
-            toks = toks[:L]
+            toks = toks[:L] if self.eos_id is None else toks[:L - 1] + [self.eos_id]
             ids[i, :len(toks)] = torch.tensor(toks)
             mask[i, :len(toks)] = 1
         return ids, mask

@@ -293,6 +293,35 @@ def test_prompt_encoder_modes():
         PromptEncoder("bert")
 
 
+def test_clip_transforms():
+    from transformers import CLIPConfig, CLIPVisionConfig
+    from teletron_b200.models.clip_transform import (CLIPTextTransform, CLIPTextWithProjectionTransform, CLIPTransform,
+                                                     preprocess_images)
+    from teletron_b200.models.text_encoders import clip_text_config
+    torch.manual_seed(0)
+    tcfg = clip_text_config(2, 32, 4, 300, 12)
+    vcfg = CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+                            patch_size=8, projection_dim=24)
+    cfg = CLIPConfig(text_config=tcfg.to_dict(), vision_config=vcfg.to_dict(), projection_dim=24)
+    images = torch.rand(2, 3, 40, 56)
+    assert preprocess_images(images, 32).shape == (2, 3, 32, 32)
+    clip = CLIPTransform(None, dtype=torch.float32, config=cfg)
+    text_f, image_f = clip(text=["a cat", "a dog on grass"], image=images)
+    assert text_f.shape == (2, 24) and image_f.shape == (2, 24)
+    assert abs(float((text_f[0] ** 2).sum()) - 1.0) < 1e-4 and abs(float((image_f[1] ** 2).sum()) - 1.0) < 1e-4   # L2-normalised
+    pooled = clip(text="a cat", text_w_proj=False, to_numpy=False)
+    assert tuple(pooled.shape) == (1, 32) and clip() is None
+    tt = CLIPTextTransform(None, dtype=torch.float32, config=tcfg)
+    assert tt(["a cat"], "after_pool").shape == (1, 32) and tt(["a cat"], "before_pool").shape == (1, 12, 32)
+    with pytest.raises(ValueError):
+        tt("a cat", "middle")
+    two = CLIPTextWithProjectionTransform(None, dtype=torch.float32, config=(tcfg, clip_text_config(2, 48, 4, 300, 12)))
+    feats, pooled = two(["a cat", "a dog"], "after_pool")
+    assert feats.shape == (2, 32 + 48) and pooled.shape == (2, 48)
+    feats, pooled = two(["a cat", "a dog"], "before_pool")
+    assert feats.shape == (2, 12, 32 + 48) and pooled.shape == (2, 48)
+
+
 # ---------------------------------------------------------------- failure detection (host side only)
 def test_step_watchdog_fires_without_heartbeat():
     from teletron_b200.training.watchdog import StepWatchdog
