@@ -322,6 +322,43 @@ def test_clip_transforms():
     assert feats.shape == (2, 12, 32 + 48) and pooled.shape == (2, 48)
 
 
+def test_legacy_fused_layer_names():
+    """The reference's module-level wrapper names, checked against plain PyTorch formulas (and their gradients)."""
+    import torch.nn.functional as F
+    from teletron_b200.legacy.fusedlayers import (AdaLNCustom, FP32LayerNorm, FusedAdaLayerNormZero,
+                                                  FusedAdaLayerNormZeroSingle, Get_RMSNorm, RMSNormModelFunction)
+    torch.manual_seed(0)
+    x = torch.randn(2, 5, 16, requires_grad=True)
+    emb = torch.randn(2, 16)
+    ln = lambda t: F.layer_norm(t, (16,), eps=1e-6)  # noqa: E731
+    zero = FusedAdaLayerNormZero(16)
+    out, gate_msa, shift_mlp, scale_mlp, gate_mlp = zero(x, emb)
+    sh, sc, g, sh2, sc2, g2 = zero.linear(F.silu(emb)).chunk(6, dim=1)
+    torch.testing.assert_close(out, ln(x) * (1 + sc[:, None]) + sh[:, None], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(gate_msa, g)
+    torch.testing.assert_close(scale_mlp, sc2)
+    out.sum().backward()
+    assert x.grad is not None and zero.linear.weight.grad is not None
+    single = FusedAdaLayerNormZeroSingle(16)
+    out, gate = single(x.detach(), emb)
+    sh, sc, g = single.linear(F.silu(emb)).chunk(3, dim=1)
+    torch.testing.assert_close(out, ln(x.detach()) * (1 + sc[:, None]) + sh[:, None], rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        AdaLNCustom(8)(x, sc, sh)
+    with pytest.raises(ValueError):
+        FusedAdaLayerNormZero(16, norm_type="batch_norm")
+    y = FP32LayerNorm(16, elementwise_affine=False)(x.detach().bfloat16())
+    assert y.dtype == torch.bfloat16 and torch.allclose(y.float(), ln(x.detach().bfloat16().float()), atol=2e-2)
+    norm = Get_RMSNorm()(16)
+    w = torch.rand(16)
+    with torch.no_grad():
+        norm.weight.copy_(w)
+    xd = x.detach()
+    ref = xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    torch.testing.assert_close(norm(xd), ref, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(RMSNormModelFunction.apply(xd, w, 1e-6), ref, rtol=1e-5, atol=1e-5)
+
+
 # ---------------------------------------------------------------- failure detection (host side only)
 def test_step_watchdog_fires_without_heartbeat():
     from teletron_b200.training.watchdog import StepWatchdog
