@@ -99,3 +99,12 @@ def get_batch_on_this_tp_cp_rank(data_iterator: Optional[Iterator], device, cons
             if batch.get("first_ref_image") is not None and batch.get("first_frame_latents") is None:
                 batch["first_frame_latents"] = encode_fn(batch["first_ref_image"].to(device)[:, None])
     return broadcast_batch(batch, device, group)
+
+
+def get_batch_on_this_tp_cp_rank_vast(data_iterator, max_length: int = 256):
+    """Entry point with the reference's name (``teletron/training/utils.py:77-82``): takes the device, the encoder-service
+    consumer (when ``--distributed-vae``) and the VAE encode function from the global arguments."""
+    from .args import get_args
+    args = get_args()
+    return get_batch_on_this_tp_cp_rank(data_iterator, args.device, consumer=getattr(args, "encoder_consumer", None),
+                                        encode_fn=getattr(args, "vae_encode_fn", None))
