@@ -87,3 +87,31 @@ def test_large_k_weight_gradient_shape():
     dw = G.gemm(dy, x, "tn")
     G.check_status()
     assert _rel(dw, dy.float().t() @ x.float()) < 6e-3
+
+
+@pytest.mark.parametrize("M,N,K,layout", [(300, 264, 192, "nt"), (130, 136, 320, "nn"), (264, 520, 200, "tn")])
+def test_output_window_is_the_only_memory_written(M, N, K, layout):
+    """The output is a window inside a larger buffer pre-filled with a guard pattern: rows above and below, and the
+    columns left and right of the window, must come back untouched (ragged last tiles must not spill)."""
+    from teletron_b200.ops import gemm_tcgen05 as G
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    if layout == "nt":
+        a, b = _mk((M, K), g), _mk((N, K), g)
+        ref = a.float() @ b.float().t()
+    elif layout == "nn":
+        a, b = _mk((M, K), g), _mk((K, N), g)
+        ref = a.float() @ b.float()
+    else:
+        a, b = _mk((K, M), g), _mk((K, N), g)
+        ref = a.float().t() @ b.float()
+    pad_r, pad_c = 5, 8                                   # the column offset keeps the window 16-byte aligned
+    guard = torch.full((M + 2 * pad_r, N + 2 * pad_c), -777.0, device="cuda", dtype=torch.bfloat16)
+    window = guard[pad_r:pad_r + M, pad_c:pad_c + N]
+    if not G.supported(a, b, layout):
+        pytest.skip("shape outside the kernel's gate")
+    G.gemm(a, b, layout, out=window)
+    G.check_status()
+    assert _rel(window, ref) < 8e-3
+    mask = torch.ones_like(guard, dtype=torch.bool)
+    mask[pad_r:pad_r + M, pad_c:pad_c + N] = False
+    assert bool((guard[mask] == -777.0).all())
