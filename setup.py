@@ -20,7 +20,7 @@ setup(
     version="0.1.0",
     description="Blackwell-native long-context video-DiT training framework with TeleTron's capabilities",
     packages=find_packages(include=["teletron_b200", "teletron_b200.*"]),
-    package_data={"teletron_b200": ["lib/*.so", "csrc/*"]},
+    package_data={"teletron_b200": ["lib/*.so", "csrc/*", "data/*.yml", "convert_ckpt/hunyuan/*.sh", "convert_ckpt/hunyuan/*.md"]},
     python_requires=">=3.10",
     install_requires=["torch>=2.6", "numpy", "pyyaml", "transformers"],
     cmdclass={"build_py": BuildWithKernels},
