@@ -253,7 +253,8 @@ def fused_comm_enabled() -> bool:
 
 def _use_fused(x: torch.Tensor, head_dim: int) -> bool:
     return (_FUSED_COMM and ps.get_context_parallel_world_size() > 1 and x.is_cuda and x.dtype == torch.bfloat16
-            and x.shape[0] == 1 and head_dim == 128 and ops.get_impl() != "torch")
+            and x.shape[0] == 1 and head_dim == 128 and ops.get_impl() != "torch"
+            and ps.group_is_single_node(ps.get_context_parallel_group()))
 
 
 _FUSED_TP_MIN_ROWS = 1024      # below this (the text stream) two device barriers cost more than the NCCL collectives
@@ -263,7 +264,8 @@ def _use_fused_tp(x: torch.Tensor, sequence_parallel: bool, activation) -> bool:
     """Sequence-parallel MLP through the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels."""
     return (_FUSED_COMM and sequence_parallel and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3
             and x.shape[0] == 1 and x.shape[1] >= _FUSED_TP_MIN_ROWS and ops.get_impl() != "torch"
-            and activation in (None, "gelu", "gelu_tanh"))
+            and activation in (None, "gelu", "gelu_tanh")
+            and ps.group_is_single_node(ps.get_tensor_model_parallel_group()))
 
 
 def _tp_workspace(rows: int, k_max: int, n_max: int):

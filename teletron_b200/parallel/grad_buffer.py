@@ -172,7 +172,9 @@ class DistributedDataParallel(nn.Module):
         self.heap = None
         self.heap_offsets = None
         storage = None
-        if fused_comm and self.world > 1 and len(by_dtype) == 1 and named[0][1].is_cuda and named[0][1].dtype == torch.bfloat16:
+        from . import state as _ps
+        if (fused_comm and self.world > 1 and len(by_dtype) == 1 and named[0][1].is_cuda and named[0][1].dtype == torch.bfloat16
+                and _ps.group_is_single_node(group)):          # peers on other hosts cannot be mapped: NCCL path
             # gradient reduce-scatter and parameter all-gather by in-kernel NVLink loads / stores: both flat
             # buffers live in a symmetric heap mapped into every data-parallel peer
             from .symm_mem import SymmetricHeap

@@ -304,6 +304,28 @@ def get_producer_pairs() -> List[CommPair]:
     return [p for p in _STATE.comm_pairs if p.producer == _STATE.rank]
 
 
+_SINGLE_NODE: Dict[int, bool] = {}
+
+
+def group_is_single_node(group) -> bool:
+    """True when every rank of ``group`` runs on this host, i.e. peer memory can be mapped through CUDA IPC.  The in-kernel
+    collectives need that; a group that spans hosts keeps the NCCL path.  Collective on first use per group (cached)."""
+    if group is None or not dist.is_initialized():
+        return True
+    key = id(group)
+    if key not in _SINGLE_NODE:
+        import socket
+        try:
+            with open("/proc/sys/kernel/random/boot_id") as f:        # two containers on one host may share a hostname
+                ident = socket.gethostname() + ":" + f.read().strip()
+        except OSError:
+            ident = socket.gethostname()
+        names = [None] * dist.get_world_size(group)
+        dist.all_gather_object(names, ident, group=group)
+        _SINGLE_NODE[key] = len(set(names)) == 1
+    return _SINGLE_NODE[key]
+
+
 def local_device() -> torch.device:
     if torch.cuda.is_available():
         return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")) % max(torch.cuda.device_count(), 1))
