@@ -403,3 +403,21 @@ def test_max_frames_proposal_stays_under_the_limit():
     assert f == 357 and m.latent_frames(f) == 90
     with pytest.raises(ValueError):
         m.propose(33, 84.0, 35, 84.0, 165.0)
+
+
+def test_memory_model_reproduces_measured_peaks_and_bounds_frames():
+    from teletron_b200.models.hunyuanvideo import hunyuan_13b
+    from teletron_b200.utils import estimate, max_frames, roofline_ms, video_tokens
+    assert video_tokens(33) == 32400 and video_tokens(129) == 118800
+    t2v, i2v = hunyuan_13b(in_channels=16), hunyuan_13b(in_channels=33)
+    one = estimate(t2v, 33, optimizer_bytes_per_param=6.0, fused_comm=False).as_gib()
+    assert abs(one["total"] - 147.2) / 147.2 < 0.03                       # 1 GPU, compact optimizer state
+    e = estimate(t2v, 33, tp=2, cp=4).as_gib()
+    assert abs(e["total"] - e["weights_grads"] - e["workspaces"] - 23.9) < 1.5   # allocator part at tp2 x cp4
+    assert abs(estimate(i2v, 129, cp=8).as_gib()["total"] - 79.9) / 79.9 < 0.03  # allocator + symmetric heaps at cp8
+    f = max_frames(i2v, 165.0, tp=1, cp=8)
+    assert f % 4 == 1 and f > 245                                         # well past the reference's 8 x H800 figure
+    assert estimate(i2v, f, cp=8).total / 2 ** 30 <= 165.0 < estimate(i2v, f + 4, cp=8).total / 2 ** 30
+    assert max_frames(t2v, 1.0) == 0
+    # a GEMM of 1e15 FLOPs is compute bound, 1 GB over NVLink takes 1.3 ms
+    assert roofline_ms(flops=1e15) > 500 and abs(roofline_ms(nvlink_bytes=1e9) - 1e3 / 770.0) < 1e-6
