@@ -196,11 +196,6 @@ class MetricLogger:
 
 
 def peak_bf16_tflops() -> float:
-    """Measured sustained bf16 peak of this pool if the driver's file is present, else nominal."""
-    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    path = os.path.join(here, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as f:
-            return float(json.load(f)["bf16_tflops_sustained"])
-    except Exception:
-        return 2250.0
+    """Sustained bf16 GEMM peak used as the MFU denominator (the measured one when the peaks file is present)."""
+    from ..utils.perf import measured_peaks
+    return measured_peaks()["bf16_tflops_sustained"]
