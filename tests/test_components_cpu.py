@@ -421,3 +421,21 @@ def test_memory_model_reproduces_measured_peaks_and_bounds_frames():
     assert max_frames(t2v, 1.0) == 0
     # a GEMM of 1e15 FLOPs is compute bound, 1 GB over NVLink takes 1.3 ms
     assert roofline_ms(flops=1e15) > 500 and abs(roofline_ms(nvlink_bytes=1e9) - 1e3 / 770.0) < 1e-6
+
+
+def test_restart_wrapper_relaunches_only_on_watchdog_exit(tmp_path):
+    import os
+    import subprocess
+    script = os.path.join(os.path.dirname(__file__), "..", "examples", "hunyuanvideo", "run_with_restart.sh")
+    counter = tmp_path / "n"
+    # exits 75 (the step watchdog's code) twice, then succeeds
+    prog = f"n=$(cat {counter} 2>/dev/null || echo 0); echo $((n+1)) > {counter}; [ $n -ge 2 ] && exit 0; exit 75"
+    env = dict(os.environ, MAX_RESTARTS="5", RESTART_DELAY="0")
+    r = subprocess.run(["bash", script, "bash", "-c", prog], env=env, capture_output=True, text=True)
+    assert r.returncode == 0 and counter.read_text().strip() == "3" and r.stderr.count("restart") >= 2
+    # an ordinary failure is final
+    r = subprocess.run(["bash", script, "bash", "-c", "exit 3"], env=env, capture_output=True, text=True)
+    assert r.returncode == 3 and "not restarting" in r.stderr
+    # the restart budget is respected
+    r = subprocess.run(["bash", script, "bash", "-c", "exit 75"], env=dict(env, MAX_RESTARTS="1"), capture_output=True, text=True)
+    assert r.returncode == 75 and "giving up" in r.stderr
