@@ -47,7 +47,7 @@ def _add_train_args(p):
     g.add_argument("--fp16", action="store_true")
     g.add_argument("--lr", type=float, default=1e-5)
     g.add_argument("--min-lr", type=float, default=0.0)
-    g.add_argument("--lr-decay-style", type=str, default="constant", choices=["constant", "linear", "cosine"])
+    g.add_argument("--lr-decay-style", type=str, default="constant", choices=["constant", "linear", "cosine", "inverse-square-root"])
     g.add_argument("--lr-decay-iters", type=int, default=None)
     g.add_argument("--lr-warmup-fraction", type=float, default=0.0)
     g.add_argument("--lr-warmup-iters", type=int, default=0)

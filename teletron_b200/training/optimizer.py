@@ -192,7 +192,7 @@ class DistributedOptimizer:
 
 
 class OptimizerParamScheduler:
-    """Learning-rate schedule: warmup then constant / linear / cosine decay (Megatron flag names)."""
+    """Learning-rate schedule: warmup then constant / linear / cosine / inverse-square-root decay (Megatron flag names)."""
 
     def __init__(self, optimizer: DistributedOptimizer, max_lr: float, min_lr: float = 0.0,
                  lr_warmup_steps: int = 0, lr_decay_steps: int = 1, lr_decay_style: str = "constant"):
@@ -208,6 +208,10 @@ class OptimizerParamScheduler:
             return self.max_lr * n / self.warmup
         if self.style == "constant":
             return self.max_lr
+        if self.style == "inverse-square-root":
+            # max_lr * sqrt(warmup) / sqrt(step), floored at min_lr (Megatron's formula; warmup 0 counts as 1)
+            w = max(self.warmup, 1)
+            return max(self.min_lr, self.max_lr * math.sqrt(w) / math.sqrt(max(n, w)))
         if n > self.decay_steps:
             return self.min_lr
         ratio = (n - self.warmup) / max(1, self.decay_steps - self.warmup)

@@ -158,6 +158,13 @@ def test_lr_schedule():
     assert abs(o.lr - 0.55) < 1e-6
     s.step(100)
     assert abs(o.lr - 0.1) < 1e-9
+    r = OptimizerParamScheduler(o, max_lr=1.0, min_lr=0.05, lr_warmup_steps=16, lr_decay_style="inverse-square-root")
+    r.step(16)
+    assert abs(o.lr - 1.0) < 1e-9
+    r.step(48)                                   # step 64: sqrt(16 / 64) = 0.5
+    assert abs(o.lr - 0.5) < 1e-9
+    r.step(100000)
+    assert abs(o.lr - 0.05) < 1e-9               # floored at min_lr
 
 
 # ---------------------------------------------------------------- data
