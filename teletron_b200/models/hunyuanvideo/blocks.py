@@ -17,6 +17,8 @@ projection GEMM + gate + residual, GEMM + GELU).
 
 from __future__ import annotations
 
+import collections
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -237,7 +239,26 @@ def _ulysses_attention(q, k, v, tq, tk, tv, pad: Optional[SeqPad], kv_valid_len:
 
 
 _FUSED_COMM = False
-_WORKSPACES = {}
+# Collective workspaces (symmetric heaps) by shape key, least recently used first.  Training uses one or two shapes; data with
+# varying clip lengths would otherwise keep a heap per length for ever, so the cache is bounded: when a new shape arrives
+# and the cache is full, the least recently used workspace is closed after a device synchronisation.  Every rank of a group
+# sees the same sequence of shapes, so all of them evict the same entry.  The bound must exceed the number of distinct
+# shapes alive inside one training step (their buffers back tensors saved for backward).
+_WORKSPACES = collections.OrderedDict()
+_MAX_WORKSPACES = int(os.environ.get("TELETRON_B200_MAX_WORKSPACES", "8"))
+
+
+def _cached_workspace(key, make):
+    ws = _WORKSPACES.get(key)
+    if ws is not None:
+        _WORKSPACES.move_to_end(key)
+        return ws
+    while len(_WORKSPACES) >= max(1, _MAX_WORKSPACES):
+        _, old = _WORKSPACES.popitem(last=False)
+        torch.cuda.synchronize()
+        old.heap.close()
+    ws = _WORKSPACES[key] = make()
+    return ws
 
 
 def set_fused_comm(enabled: bool) -> None:
@@ -270,20 +291,13 @@ def _use_fused_tp(x: torch.Tensor, sequence_parallel: bool, activation) -> bool:
 
 def _tp_workspace(rows: int, k_max: int, n_max: int):
     from ...ops.fused_comm import TPWorkspace
-    key = ("tp", rows, k_max, n_max)
-    ws = _WORKSPACES.get(key)
-    if ws is None:
-        ws = _WORKSPACES[key] = TPWorkspace(ps.get_tensor_model_parallel_group(), rows, max(k_max, n_max), max(k_max, n_max))
-    return ws
+    width = max(k_max, n_max)
+    return _cached_workspace(("tp", rows, width), lambda: TPWorkspace(ps.get_tensor_model_parallel_group(), rows, width, width))
 
 
 def _workspace(heads_local: int, s: int, T: int):
     from ...ops.fused_comm import UlyssesWorkspace
-    key = (heads_local, s, T)
-    ws = _WORKSPACES.get(key)
-    if ws is None:
-        ws = _WORKSPACES[key] = UlyssesWorkspace(ps.get_context_parallel_group(), heads_local, s, T)
-    return ws
+    return _cached_workspace((heads_local, s, T), lambda: UlyssesWorkspace(ps.get_context_parallel_group(), heads_local, s, T))
 
 
 def _fused_kv_len(ws, pad: Optional[SeqPad], kv_valid_len) -> Optional[int]:
