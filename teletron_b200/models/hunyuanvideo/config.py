@@ -44,6 +44,7 @@ class HunyuanParams:
     recompute_method: str = "block"                  # "block" | "uniform"
     recompute_num_layers: Optional[int] = None       # None = every block (reference behaviour)
     sequence_parallel: bool = False                  # shard the residual stream's tokens over tensor-parallel ranks
+    sequence_pad_multiple: int = 8                   # local video tokens are padded to a multiple of this (GEMM K / TMA alignment of the weight gradients)
     sequence_parallel_row_multiple: int = 1          # token blocks are padded to a multiple of this (128 for the fused TP kernels)
     recompute_save_attention: bool = False           # keep attention (out, lse) so the recompute pass skips that kernel
     fused_kernels: bool = True

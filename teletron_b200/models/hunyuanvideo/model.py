@@ -161,7 +161,10 @@ class HunyuanVideoTransformer3DModel(nn.Module):
             raise ValueError(f"sequence parallelism needs the video token count {x.shape[1]} divisible by tp = {self.tp}")
         if cp > 1:
             # with sequence parallelism each context-parallel chunk is cut once more into tp token blocks
-            pad = SeqPad.for_length(x.shape[1], cp * self.tp * cfg.sequence_parallel_row_multiple if sp else cp)
+            # every rank's chunk is a multiple of sequence_pad_multiple tokens: the token count is the K dim of the weight-
+            # gradient GEMMs, which the tensor-core kernel takes in multiples of 8
+            per_rank = cfg.sequence_pad_multiple * (self.tp * cfg.sequence_parallel_row_multiple if sp else 1)
+            pad = SeqPad.for_length(x.shape[1], cp * max(1, per_rank))
             x = M.split_forward_gather_backward(pad.add(x, 1), cp_group, dim=1, grad_scale="down")
             cos = M.split_forward_gather_backward(pad.add(cos, 0), cp_group, dim=0, grad_scale="down")
             sin = M.split_forward_gather_backward(pad.add(sin, 0), cp_group, dim=0, grad_scale="down")
