@@ -50,6 +50,7 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-save-attention", action="store_true")
     p.add_argument("--fused-comm", type=int, default=1, help="1: in-kernel NVLink collectives for context parallelism")
+    p.add_argument("--seq-pad-multiple", type=int, default=8, help="pad each context-parallel chunk to a multiple of this many tokens")
     p.add_argument("--overlap-grad-reduce", type=int, default=0,
                    help="1: bucketed gradient reduce-scatter on a side stream during backward")
     p.add_argument("--sequence-parallel", type=int, default=0,
@@ -180,7 +181,8 @@ def main():
     cfg = hunyuan_13b(in_channels=33 if a.model_type == "i2v" else 16, num_layers=a.layers,
                       num_single_layers=a.single_layers,
                       recompute_granularity=None if a.no_recompute else "full", seed=1234,
-                      recompute_save_attention=not a.no_save_attention and a.impl == "ours", sequence_parallel=sp)
+                      recompute_save_attention=not a.no_save_attention and a.impl == "ours", sequence_parallel=sp,
+                      sequence_pad_multiple=a.seq_pad_multiple)
     if a.impl == "ours" and a.fused_comm and a.gpus > 1:
         from teletron_b200.models.hunyuanvideo import blocks
         blocks.set_fused_comm(True)

@@ -31,7 +31,7 @@ def build_config(args):
     kw = dict(recompute_granularity=args.recompute_granularity, recompute_method=args.recompute_method,
               recompute_num_layers=None, init_method_std=args.init_method_std, seed=args.seed,
               apply_text_mask=args.apply_text_mask, recompute_save_attention=args.recompute_save_attention,
-              sequence_parallel=bool(args.sequence_parallel))
+              sequence_parallel=bool(args.sequence_parallel), sequence_pad_multiple=args.sequence_pad_multiple)
     if args.model_size != "tiny":
         kw["in_channels"] = 33 if args.model_type == "i2v" else 16
     cfg = make(**kw).apply_env_overrides()

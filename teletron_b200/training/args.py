@@ -79,6 +79,8 @@ def _add_parallel_args(p):
     g.add_argument("--tensor-model-parallel-size", type=int, default=1)
     g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
     g.add_argument("--context-parallel-size", type=int, default=1)
+    g.add_argument("--sequence-pad-multiple", type=int, default=8,
+                   help="pad every context-parallel chunk of video tokens to a multiple of this (keeps weight-gradient GEMMs on the tensor-core kernel)")
     g.add_argument("--sequence-parallel", action="store_true",
                    help="shard activations over TP between GEMMs (all-gather->GEMM / GEMM->reduce-scatter)")
     g.add_argument("--fused-comm", action="store_true",
