@@ -50,7 +50,9 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-save-attention", action="store_true")
     p.add_argument("--fused-comm", type=int, default=1, help="1: in-kernel NVLink collectives for context parallelism")
-    p.add_argument("--seq-pad-multiple", type=int, default=8, help="pad each context-parallel chunk to a multiple of this many tokens")
+    p.add_argument("--seq-pad-multiple", type=int, default=1,
+                   help="pad each context-parallel chunk to a multiple of this many tokens (8 keeps the weight-gradient GEMMs of "
+                        "cp4 / cp8 runs on the tcgen05 kernel; 1 = the layout of the recorded multi-GPU numbers)")
     p.add_argument("--overlap-grad-reduce", type=int, default=0,
                    help="1: bucketed gradient reduce-scatter on a side stream during backward")
     p.add_argument("--sequence-parallel", type=int, default=0,
