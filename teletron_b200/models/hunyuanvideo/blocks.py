@@ -255,8 +255,9 @@ def _cached_workspace(key, make):
         return ws
     while len(_WORKSPACES) >= max(1, _MAX_WORKSPACES):
         _, old = _WORKSPACES.popitem(last=False)
-        torch.cuda.synchronize()
-        old.heap.close()
+        # the last kernels that used the workspace touch the peers' slabs without a closing barrier: a rank may only
+        # free its slab once every peer's work on it has finished, and only after the peers have unmapped it
+        old.heap.close(collective=True)
     ws = _WORKSPACES[key] = make()
     return ws
 

@@ -114,18 +114,22 @@ class HunyuanVideoTransformer3DModel(nn.Module):
                             x, ctx = b(x, ctx, temb, cos, sin, pad, kv_valid_len)
                         return x, ctx
                     return fn
-                for start in range(0, n, chunk):
-                    x, ctx = checkpoint(run(start, min(n, start + chunk)), x, ctx, temb, cos, sin,
-                                        use_reentrant=False, preserve_rng_state=False)
-                return x, ctx
-            limit = n if cfg.recompute_num_layers is None else min(n, cfg.recompute_num_layers)
+                if chunk > 1:
+                    # several blocks per checkpoint: tensors that the fused collective ops save are private copies here,
+                    # since a later block's replay would overwrite the shared workspace before an earlier block's backward
+                    for start in range(0, n, chunk):
+                        x, ctx = checkpoint(run(start, min(n, start + chunk)), x, ctx, temb, cos, sin,
+                                            use_reentrant=False, preserve_rng_state=False)
+                    return x, ctx
+                limit = n
+            else:
+                limit = n if cfg.recompute_num_layers is None else min(n, cfg.recompute_num_layers)
+            from ...training.recompute import checkpoint_block
             for i, b in enumerate(blocks):
-                if i < limit and cfg.recompute_save_attention:
-                    from ...training.recompute import checkpoint_block
-                    x, ctx = checkpoint_block(b, (x, ctx, temb, cos, sin), (pad, kv_valid_len), save_attention=True)
-                elif i < limit:
-                    x, ctx = checkpoint(b, x, ctx, temb, cos, sin, pad, kv_valid_len,
-                                        use_reentrant=False, preserve_rng_state=False)
+                if i < limit:
+                    # one block per checkpoint: its replay is followed at once by its backward
+                    x, ctx = checkpoint_block(b, (x, ctx, temb, cos, sin), (pad, kv_valid_len),
+                                              save_attention=bool(cfg.recompute_save_attention))
                 else:
                     x, ctx = b(x, ctx, temb, cos, sin, pad, kv_valid_len)
             return x, ctx

@@ -19,6 +19,7 @@ synchronisation point to turn a timed-out barrier into :class:`CommTimeoutError`
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Optional, Tuple
 
@@ -27,7 +28,8 @@ import torch.distributed as dist
 
 from ..parallel.symm_mem import SymmetricHeap
 from . import _lib, gemm
-from ._lib import c_float, c_int, c_long, call, check, ptr, stream
+from ._lib import c_float, c_int, c_long, check, ptr, stream
+from ._lib import call as _call
 from .gemm_tcgen05 import status_tensor
 
 BF16 = torch.bfloat16
@@ -35,6 +37,43 @@ BF16 = torch.bfloat16
 
 def _table(ptrs):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+# Every layer of a model shares one workspace per shape, and q / k / v and the gathered attention output are views
+# of that workspace.  Tensors saved for backward may therefore alias it only while nothing else can run between the
+# forward that wrote them and the backward that reads them: that is the replay of ONE checkpointed block, which is
+# followed at once by that block's backward.  Everywhere else (no recompute, layers beyond --recompute-num-layers,
+# a uniform chunk of several blocks) the next layer's forward would overwrite them behind autograd's back, so the
+# ops below save private copies instead.
+_SINGLE_BLOCK_REPLAY = 0
+COUNTERS = {"qkv_gemm_fused": 0, "attn_fwd_push": 0, "gemm_comm": 0, "gemm_ag": 0, "private_saves": 0}
+
+
+_COUNTED = {"tt_qkv_gemm_fused": "qkv_gemm_fused", "tt_attn_fwd_push": "attn_fwd_push", "tt_gemm_comm_bf16": "gemm_comm",
+            "tt_gemm_ag_bf16": "gemm_ag"}
+
+
+def call(fn_name: str, *args) -> None:
+    """Native call that also counts the fused compute + collective launches by kind (reported by the benchmark)."""
+    k = _COUNTED.get(fn_name)
+    if k is not None:
+        COUNTERS[k] += 1
+    _call(fn_name, *args)
+
+
+@contextlib.contextmanager
+def single_block_replay():
+    """Entered by the block checkpoint while it re-runs exactly one block for that block's own backward."""
+    global _SINGLE_BLOCK_REPLAY
+    _SINGLE_BLOCK_REPLAY += 1
+    try:
+        yield
+    finally:
+        _SINGLE_BLOCK_REPLAY -= 1
+
+
+def saves_need_private_copies() -> bool:
+    return torch.is_grad_enabled() and _SINGLE_BLOCK_REPLAY == 0
 
 
 class UlyssesWorkspace:
@@ -173,13 +212,21 @@ def _a2a_gemm(ws: UlyssesWorkspace, src_name: str, row_off: int, M: int, w, bias
     return out
 
 
+def _gather_heads(ws: UlyssesWorkspace, rows: int, row_off: int) -> torch.Tensor:
+    """``[rows, cp * span]``: every rank's head columns of ``o`` for ``rows`` tokens starting at ``row_off`` (peer loads)."""
+    span = ws.h_loc * 128
+    a = torch.empty(rows, ws.cp * span, dtype=BF16, device=ws.heap.device)
+    call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(rows), c_int(span), c_long(row_off), ptr(a), stream())
+    return a
+
+
 class _FusedAllToAllLinear(torch.autograd.Function):
     """``y_video = gather_heads(o)[rank's tokens] @ W^T + b`` and ``y_text = gather_heads(o)[text] @ Wt^T + bt`` with the
     gather fused into the GEMM operand fetch.  ``extra`` / ``extra_t`` are optional local tensors concatenated to
     the gathered heads along K (the MLP half of the single block's merged projection)."""
 
     @staticmethod
-    def forward(ctx, ws, o, w, b, wt, bt, extra, extra_t):
+    def forward(ctx, ws, private, o, w, b, wt, bt, extra, extra_t):
         dst = ws.token_major("o")
         ws.heap.barrier()                      # peers are done with the previous contents of `o`
         if o.data_ptr() != dst.data_ptr():
@@ -190,7 +237,12 @@ class _FusedAllToAllLinear(torch.autograd.Function):
         y = _a2a_gemm(ws, "o", ws.video_off + ws.rank * ws.s, ws.s, w, b, ex)
         yt = _a2a_gemm(ws, "o", ws.text_off, ws.T, wt, bt, ext)
         ctx.ws = ws
-        ctx.save_for_backward(w, wt, ex, ext)
+        a = at = None
+        if private and any(ctx.needs_input_grad):
+            # the weight gradients need the gathered activations; `o` of the workspace will not survive the next layer
+            COUNTERS["private_saves"] += 1
+            a, at = _gather_heads(ws, ws.s, ws.video_off + ws.rank * ws.s), _gather_heads(ws, ws.T, ws.text_off)
+        ctx.save_for_backward(w, wt, ex, ext, a, at)
         ctx.has = (b is not None, bt is not None, extra is not None, extra_t is not None)
         ctx.extra_shapes = (None if extra is None else extra.shape, None if extra_t is None else extra_t.shape)
         return y.view(1, ws.s, -1), yt.view(1, ws.T, -1)
@@ -198,18 +250,16 @@ class _FusedAllToAllLinear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dyt):
         ws: UlyssesWorkspace = ctx.ws
-        w, wt, ex, ext = ctx.saved_tensors
+        w, wt, ex, ext, a, at = ctx.saved_tensors
         hb, hbt, hex_, hext = ctx.has
         span = ws.h_loc * 128
         G = ws.cp * span                                        # gathered K columns
         dy2 = check(dy.reshape(ws.s, -1).contiguous(), BF16, "dy")
         dyt2 = check(dyt.reshape(ws.T, -1).contiguous(), BF16, "dyt")
         dev = dy2.device
-        # weight gradients need the gathered activations: collect them with the peer-reading copy kernel
-        a = torch.empty(ws.s, G, dtype=BF16, device=dev)
-        call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(ws.s), c_int(span), c_long(ws.video_off + ws.rank * ws.s), ptr(a), stream())
-        at = torch.empty(ws.T, G, dtype=BF16, device=dev)
-        call("tt_gather_cols_bf16", ws.table("o"), c_int(ws.cp), c_long(ws.T), c_int(span), c_long(ws.text_off), ptr(at), stream())
+        if a is None:
+            # weight gradients need the gathered activations: collect them with the peer-reading copy kernel
+            a, at = _gather_heads(ws, ws.s, ws.video_off + ws.rank * ws.s), _gather_heads(ws, ws.T, ws.text_off)
         a_full = a if ex is None else torch.cat([a, ex], dim=1)
         at_full = at if ext is None else torch.cat([at, ext], dim=1)
         dw = gemm.gemm_tn(dy2, a_full)
@@ -230,13 +280,13 @@ class _FusedAllToAllLinear(torch.autograd.Function):
         do_local[0, ws.text_off:ws.text_off + ws.T, :].copy_(dot_full[:, ws.rank * span:(ws.rank + 1) * span] * float(ws.cp))
         dext = dot_full[:, G:].contiguous().view(ctx.extra_shapes[1]) if hext else None
         ws.heap.barrier()                      # all pushed gradient tiles have landed
-        return (None, do_local, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
+        return (None, None, do_local, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
 
 
 def fused_a2a_linear(ws: UlyssesWorkspace, o, w, b, wt, bt, extra=None, extra_t=None):
     """``o [1, S_tot, heads/cp * 128]`` (this rank's heads, all tokens) -> projections of this rank's video tokens
     (weights ``w``) and of the replicated text tokens (weights ``wt``)."""
-    return _FusedAllToAllLinear.apply(ws, o, w, b, wt, bt, extra, extra_t)
+    return _FusedAllToAllLinear.apply(ws, saves_need_private_copies(), o, w, b, wt, bt, extra, extra_t)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -263,7 +313,7 @@ class _FusedAttentionOutProj(torch.autograd.Function):
     followed by the local output projections of the video and the text stream."""
 
     @staticmethod
-    def forward(ctx, ws, kv_len, scale, q, k, v, w, b, wt, bt, extra, extra_t):
+    def forward(ctx, ws, kv_len, scale, private, q, k, v, w, b, wt, bt, extra, extra_t):
         from . import attn_tcgen05 as A
         import math
         H_all = ws.heads
@@ -298,6 +348,10 @@ class _FusedAttentionOutProj(torch.autograd.Function):
         y = _local_gemm_extra(ws, g[T:], ex, w, b)
         yt = _local_gemm_extra(ws, g[:T], ext, wt, bt)
         ctx.ws, ctx.sc, ctx.kvl = ws, sc, kvl
+        if private and any(ctx.needs_input_grad):
+            # q / k / v and g live in the workspace every layer shares: keep copies that the next layer cannot overwrite
+            COUNTERS["private_saves"] += 1
+            q, k, v, g = q.clone(), k.clone(), v.clone(), g.clone()
         ctx.save_for_backward(q, k, v, out, lse, w, wt, ex, ext, g)
         ctx.has = (b is not None, bt is not None)
         ctx.extra_shapes = (None if extra is None else extra.shape, None if extra_t is None else extra_t.shape)
@@ -342,13 +396,13 @@ class _FusedAttentionOutProj(torch.autograd.Function):
         ws.heap.barrier()                  # all pushed gradient tiles have landed
         dq, dk, dv = attn_backward.backward(do_local, q, k, v, out, lse, ctx.sc, ctx.kvl)
         del dwt_same
-        return (None, None, None, dq, dk, dv, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
+        return (None, None, None, None, dq, dk, dv, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
 
 
 def fused_attention_outproj(ws: UlyssesWorkspace, q, k, v, w, b, wt, bt, extra=None, extra_t=None, kv_len=None, scale=None):
     """``q, k, v [1, heads/cp, T + cp*s, 128]`` -> (projection of this rank's video tokens with ``w``, projection of the
     text tokens with ``wt``); ``extra`` / ``extra_t`` are local tensors concatenated to the attention output along K."""
-    return _FusedAttentionOutProj.apply(ws, kv_len, scale, q, k, v, w, b, wt, bt, extra, extra_t)
+    return _FusedAttentionOutProj.apply(ws, kv_len, scale, saves_need_private_copies(), q, k, v, w, b, wt, bt, extra, extra_t)
 
 
 # ---------------------------------------------------------------------------------------------

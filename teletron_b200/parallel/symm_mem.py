@@ -15,6 +15,7 @@ The reference has no equivalent: every collective there is an NCCL call
 from __future__ import annotations
 
 import ctypes
+import weakref
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -37,6 +38,13 @@ def _as_tensor(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
 
 
 ALLOCATED_BYTES = 0      # bytes of symmetric heaps this process holds (outside the PyTorch caching allocator)
+LIVE_HEAPS: "weakref.WeakSet[SymmetricHeap]" = weakref.WeakSet()     # read by the per-step status check
+
+
+def set_barrier_timeout_seconds(seconds: float) -> None:
+    """Budget of every device-side barrier created from now on (GPU clock taken as 2 GHz)."""
+    global DEFAULT_TIMEOUT_CYCLES
+    DEFAULT_TIMEOUT_CYCLES = max(1, int(seconds * 2e9))
 
 
 class SymmetricHeap:
@@ -73,6 +81,7 @@ class SymmetricHeap:
         self._status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._views: Dict[Tuple[int, int], torch.Tensor] = {}
         self.timeout_cycles = DEFAULT_TIMEOUT_CYCLES
+        LIVE_HEAPS.add(self)
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, nbytes: int) -> int:
@@ -120,7 +129,21 @@ class SymmetricHeap:
             self._status.zero_()
             raise _lib.CommTimeoutError(f"symmetric-heap barrier timed out on rank {self.rank} (status {code})")
 
-    def close(self) -> None:
+    def close(self, collective: bool = False) -> None:
+        """Unmap the peers' slabs and free this rank's.  ``collective=True`` (every rank of the group calls it at the same
+        point of the program): wait for this GPU's work, meet the peers so that none of their kernels still touches this
+        slab, unmap, meet again so that nobody frees a slab that is still mapped elsewhere, then free."""
+        LIVE_HEAPS.discard(self)
+        if collective and self.world > 1 and self.local_ptr:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            for p in self._opened:
+                try:
+                    call("tt_ipc_close", ctypes.c_void_p(p))
+                except Exception:
+                    pass
+            self._opened = []
+            dist.barrier(group=self.group)
         for p in self._opened:
             try:
                 call("tt_ipc_close", ctypes.c_void_p(p))
@@ -143,9 +166,6 @@ def get_heap(group, nbytes: int) -> SymmetricHeap:
     h = _HEAPS.get(key)
     if h is None or h.nbytes < nbytes + FLAG_BYTES:
         if h is not None:
-            torch.cuda.synchronize()
-            if group is not None:
-                dist.barrier(group=group)
-            h.close()
+            h.close(collective=True)
         h = _HEAPS[key] = SymmetricHeap(group, nbytes)
     return h

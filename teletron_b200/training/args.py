@@ -85,6 +85,12 @@ def _add_parallel_args(p):
                    help="shard activations over TP between GEMMs (all-gather->GEMM / GEMM->reduce-scatter)")
     g.add_argument("--fused-comm", action="store_true",
                    help="use the in-kernel NVLink collectives (fused Ulysses all-to-all, AG-GEMM, GEMM-RS)")
+    g.add_argument("--comm-barrier-timeout-seconds", type=float, default=10.0,
+                   help="budget of every device-side barrier of the in-kernel collectives; when it runs out the kernel "
+                        "records a status word and returns")
+    g.add_argument("--comm-check-interval", type=int, default=1,
+                   help="read the kernels' status words every N steps, after the gradient sync and before the optimizer "
+                        "update (one small all-reduce and one host read); 0 = never")
     g.add_argument("--distributed-backend", type=str, default=None, choices=[None, "nccl", "gloo"])
     g.add_argument("--distributed-timeout-minutes", type=float, default=10)
     g.add_argument("--distributed-vae", action="store_true")

@@ -31,6 +31,7 @@ from .checkpoint import load_checkpoint, save_checkpoint
 from .logging import MetricLogger, Timers, model_flops_per_sample, peak_bf16_tflops, print_rank_0, print_rank_last
 from .optimizer import DistributedOptimizer, OptimizerParamScheduler
 from ..ops import nvtx_range
+from ..ops._lib import CommTimeoutError
 from .watchdog import StepWatchdog
 
 _TIMERS: Optional[Timers] = None
@@ -89,7 +90,9 @@ def initialize(extra_args_provider: Optional[Callable] = None, argv=None, args_d
         set_random_seed(args.seed, args.data_parallel_random_init)
     if args.fused_comm:
         from ..models.hunyuanvideo import blocks
+        from ..parallel import symm_mem
         blocks.set_fused_comm(True)
+        symm_mem.set_barrier_timeout_seconds(args.comm_barrier_timeout_seconds)
     args.device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
     return args
 
@@ -151,6 +154,13 @@ def train_step(forward_step_func, data_iterator, model: DistributedDataParallel,
     with nvtx_range("grad-sync"):
         model.finish_grad_sync()
     timers("grad-sync").stop()
+    if getattr(args, "comm_check_interval", 1) and _STEP_COUNTER[0] % max(1, getattr(args, "comm_check_interval", 1)) == 0:
+        # a bounded device-side wait that ran out (a peer that stalled or left) has left this step's activations or
+        # gradients incomplete: find out here, on every rank together, before the update is applied
+        from ..ops import status as _status
+        group = ps.get_transformer_model_group() if ps.model_parallel_is_initialized() else None
+        _status.check_all(group, what=f"training step {_STEP_COUNTER[0]}")
+    _STEP_COUNTER[0] += 1
     timers("optimizer", log_level=1).start()
     with nvtx_range("optimizer"):
         ok = optimizer.step()
@@ -159,6 +169,39 @@ def train_step(forward_step_func, data_iterator, model: DistributedDataParallel,
         scheduler.step(1)
     avg = {k: torch.stack([t.float().reshape(()) for t in v]).mean() for k, v in losses.items()}
     return avg, (0 if ok else 1), optimizer.last_grad_norm
+
+
+_STEP_COUNTER = [0]
+
+
+class _Peekable:
+    """Iterator that can say whether another item exists (it keeps one item fetched ahead)."""
+
+    _END = object()
+
+    def __init__(self, it):
+        self._it = iter(it)
+        self._next = None
+        self._primed = False
+
+    def _prime(self):
+        if not self._primed:
+            self._next = next(self._it, self._END)
+            self._primed = True
+
+    def has_next(self) -> bool:
+        self._prime()
+        return self._next is not self._END
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        self._prime()
+        if self._next is self._END:
+            raise StopIteration
+        item, self._primed = self._next, False
+        return item
 
 
 class _nullcontext:
@@ -192,8 +235,20 @@ def evaluate(forward_step_func, data_iterator, model, args, max_iters: Optional[
     saved_step = getattr(inner, "step", None)
     if saved_step is not None:
         inner.step = 1_000_000_007        # a fixed stream of its own: every validation sees the same noise and timesteps
+    if data_iterator is not None and not isinstance(data_iterator, _Peekable):
+        data_iterator = _Peekable(data_iterator)
+    group = ps.get_transformer_model_group() if (ps.model_parallel_is_initialized() and dist.is_initialized()) else None
     with torch.no_grad():
         for _ in range(n):
+            # Only the source rank of a TP x CP block holds the iterator; the others are already inside the batch broadcast
+            # when it runs dry.  So the ranks agree BEFORE every batch: the minimum over the job of "I still have one".
+            more = 1 if (data_iterator is None or data_iterator.has_next()) else 0
+            if group is not None and dist.get_world_size(group) > 1:
+                t = torch.tensor([more], dtype=torch.int32, device=args.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+                more = int(t.item())
+            if not more:
+                break
             try:
                 out, loss_func = forward_step_func(data_iterator, model)
             except StopIteration:
@@ -215,6 +270,8 @@ def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, a
     the other ranks (which take part through the batch broadcast) must be told."""
     if do_valid is None:
         do_valid = valid_data_iterator is not None
+    if valid_data_iterator is not None:
+        valid_data_iterator = _Peekable(valid_data_iterator)      # one wrapper for the whole run: it holds an item fetched ahead
     timers = get_timers()
     logger = MetricLogger(args.jsonl_log, args.tensorboard_dir, args.tensorboard_queue_size,
                           wandb_project=getattr(args, "wandb_project", None), wandb_name=getattr(args, "wandb_exp_name", None),
@@ -235,7 +292,16 @@ def train(forward_step_func, model, optimizer, scheduler, train_data_iterator, a
         if watchdog:
             watchdog.beat(iteration)
         timers("interval-time", log_level=0).start()
-        losses, skipped, grad_norm = train_step(forward_step_func, train_data_iterator, model, optimizer, scheduler, args)
+        try:
+            losses, skipped, grad_norm = train_step(forward_step_func, train_data_iterator, model, optimizer, scheduler, args)
+        except CommTimeoutError as e:
+            # every rank raises at the same point (the status is agreed on over the job): leave with the watchdog's exit
+            # code so that the restart wrapper relaunches from the last checkpoint
+            print(f"[rank {args.rank}] {e}", flush=True)
+            if watchdog:
+                watchdog.stop()
+            logger.close()
+            raise SystemExit(75)
         timers("interval-time").stop()
         iteration += 1
         skipped_total += skipped

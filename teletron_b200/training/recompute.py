@@ -16,7 +16,7 @@ from typing import Callable, List
 
 import torch
 
-from ..ops import attn_tcgen05
+from ..ops import attn_tcgen05, fused_comm
 
 
 class _CheckpointBlock(torch.autograd.Function):
@@ -39,7 +39,9 @@ class _CheckpointBlock(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         tensors = [t.detach().requires_grad_(r) for t, r in zip(ctx.saved_tensors, ctx.requires)]
-        with torch.enable_grad():
+        # the replay of this one block is followed at once by its backward: tensors saved by the fused collective ops
+        # may alias the workspace that all layers share
+        with torch.enable_grad(), fused_comm.single_block_replay():
             if ctx.save_attention:
                 with attn_tcgen05.attention_cache(ctx.cache, "replay"):
                     outs = ctx.run_fn(*tensors, *ctx.extra)

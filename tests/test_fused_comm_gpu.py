@@ -213,6 +213,50 @@ def test_fused_ulysses_model_matches_nccl_path():
     """, timeout=900)
 
 
+def test_fused_ulysses_several_layers_without_per_block_recompute():
+    """Two dual + two single blocks, cp = 2, first without recompute and then with two blocks per checkpoint: every layer
+    shares one collective workspace, so the tensors that the fused ops save for backward must be private copies; loss and
+    gradients against the NCCL all_to_all path."""
+    _run_ranks("""
+        from teletron_b200.models.hunyuanvideo import FlowConfig, HunyuanPipeline, hunyuan_13b
+        from teletron_b200.models.hunyuanvideo import blocks
+        from teletron_b200.ops import fused_comm as FC
+        from teletron_b200.parallel import state as ps
+        from teletron_b200.parallel.grad_buffer import DistributedDataParallel
+        ps.initialize_model_parallel(1, 2)
+        gen = torch.Generator().manual_seed(0)
+        batch = {"latents": torch.randn(1, 16, 3, 30, 34, generator=gen), "prompt_embeds": torch.randn(1, 40, 4096, generator=gen),
+                 "clip_text_embed": torch.randn(1, 768, generator=gen)}
+        for kw in (dict(recompute_granularity=None), dict(recompute_granularity="full", recompute_method="uniform", recompute_num_layers=2)):
+            cfg = hunyuan_13b(in_channels=16, num_layers=2, num_single_layers=2, **kw)
+            res = {}
+            for fused in (True, False):
+                blocks.set_fused_comm(fused)
+                saves0 = FC.COUNTERS["private_saves"]
+                pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"), device=torch.device("cuda", rank), dtype=torch.bfloat16)
+                ddp = DistributedDataParallel(pipe, ps.get_data_parallel_group(with_context_parallel=True))
+                ddp.zero_grad_buffer()
+                pipe.step = 0
+                loss = pipe(batch)[0]
+                loss.backward()
+                res[fused] = (float(loss.detach()), {n: p.grad.float().clone() for n, p in pipe.transformer.named_parameters() if p.grad is not None})
+                if fused:
+                    assert FC.COUNTERS["private_saves"] > saves0, "no private copies were taken"
+                del pipe, ddp
+            assert abs(res[True][0] - res[False][0]) < 2e-2 * abs(res[False][0]), (kw, res[True][0], res[False][0])
+            bad = []
+            for n, gref in res[False][1].items():
+                if n.endswith("to_k.bias"):
+                    continue
+                r = rel(res[True][1][n], gref)
+                if r > 0.08:
+                    bad.append((n, r))
+            assert not bad, (kw, bad[:8])
+        from teletron_b200.ops.gemm_tcgen05 import check_status
+        check_status()
+    """, timeout=900)
+
+
 def test_sequence_parallel_model_fused_matches_plain_tensor_parallel():
     """One dual + one single block at full width, tp = 2: token-sharded residual stream with the fused all-gather -> GEMM /
     GEMM -> reduce-scatter MLPs against plain tensor parallelism (replicated activations, NCCL all-reduce)."""
