@@ -50,9 +50,12 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-save-attention", action="store_true")
     p.add_argument("--fused-comm", type=int, default=1, help="1: in-kernel NVLink collectives for context parallelism")
-    p.add_argument("--seq-pad-multiple", type=int, default=1,
+    p.add_argument("--seq-pad-multiple", type=int, default=8,
                    help="pad each context-parallel chunk to a multiple of this many tokens (8 keeps the weight-gradient GEMMs of "
-                        "cp4 / cp8 runs on the tcgen05 kernel; 1 = the layout of the recorded multi-GPU numbers)")
+                        "cp4 / cp8 runs on the tcgen05 kernel; the pad keys are masked)")
+    p.add_argument("--breakdown", type=str, default=None,
+                   help="after the timed loops, run one more step with per-kernel-family device timing (CUDA events around "
+                        "every native call and NCCL section) and write the table to this file")
     p.add_argument("--overlap-grad-reduce", type=int, default=0,
                    help="1: bucketed gradient reduce-scatter on a side stream during backward")
     p.add_argument("--sequence-parallel", type=int, default=0,
@@ -123,6 +126,71 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_breakdown(step_fn, dev):
+    """One extra training step with CUDA events around every native call and NCCL / optimizer section.  Returns
+    ``{"step_ms": ..., "phases": {name: (ms on this rank, launches, max ms over ranks)}}`` (rank 0 writes it)."""
+    import torch
+    import torch.distributed as dist
+    from teletron_b200.ops import _lib
+    step_fn()                                    # one untimed step so that nothing of the timed loops is still in flight
+    torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _lib.profile_start()
+    e0.record()
+    step_fn()
+    e1.record()
+    prof = _lib.profile_stop()
+    step_ms = e0.elapsed_time(e1)
+    names = sorted(prof)
+    mine = torch.tensor([prof[n][0] for n in names] + [step_ms], dtype=torch.float64, device=dev)
+    worst = mine.clone()
+    if dist.is_initialized():
+        # the ranks run the same program, so the same names in the same order
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {"step_ms": float(mine[-1]), "step_ms_max": float(worst[-1]),
+            "phases": {n: (prof[n][0], prof[n][1], float(worst[i])) for i, n in enumerate(names)}}
+
+
+_FAMILIES = (("attention forward", ("tt_attn_fwd",)), ("attention backward", ("tt_attn_bwd",)),
+             ("QKV GEMM + norm + RoPE + seq->head exchange (F1)", ("tt_qkv_gemm_fused",)),
+             ("QKV backward: head->seq gather + RoPE^T + norm backward (F1b)", ("tt_qkv_post_bwd",)),
+             ("GEMMs with a fused collective (F2b push, F3)", ("tt_gemm_comm", "tt_gemm_ag")),
+             ("plain GEMMs", ("tt_gemm_bf16",)), ("QKV post-processing (unfused path)", ("tt_qkv_post_fwd",)),
+             ("device barriers (includes waiting for the slowest peer)", ("tt_comm_barrier",)),
+             ("norm / modulation / gate / GELU", ("tt_ln_mod", "tt_gate_residual", "tt_rmsnorm", "tt_gelu")),
+             ("gradient reduce-scatter + parameter all-gather (own kernels)", ("tt_reduce_scatter", "tt_all_gather_push", "tt_rs_adamw")),
+             ("AdamW", ("tt_adamw",)), ("peer copies / partial sums", ("tt_gather_cols", "tt_partial_sum")),
+             ("NCCL tensor-parallel all-reduce", ("nccl tp",)), ("NCCL other", ("nccl",)))
+
+
+def format_breakdown(b, line) -> str:
+    """Text table: device time per kernel family of one training step, and what is left (PyTorch eager ops, host gaps)."""
+    rows, used = [], set()
+    for title, prefixes in _FAMILIES:
+        ms = n = mx = 0
+        for name, (t, c, w) in b["phases"].items():
+            if name not in used and any(name.startswith(p) for p in prefixes):
+                used.add(name)
+                ms, n, mx = ms + t, n + c, mx + w
+        if n:
+            rows.append((title, ms, n, mx))
+    for name, (t, c, w) in b["phases"].items():
+        if name not in used:
+            rows.append((name, t, c, w))
+    total = sum(r[1] for r in rows)
+    out = [f"per-phase device time of one training step (CUDA events around every native call / NCCL section; rank 0 and max over ranks)",
+           f"config: {json.dumps(line['config'])}",
+           f"step: {b['step_ms']:.1f} ms on rank 0 ({b['step_ms_max']:.1f} ms max over ranks); timed loop: {line['ms_per_step']:.1f} ms/step",
+           f"{'phase':<72}{'ms':>10}{'share':>8}{'calls':>8}{'max ms':>10}"]
+    for title, ms, n, mx in sorted(rows, key=lambda r: -r[1]):
+        out.append(f"{title:<72}{ms:>10.2f}{100 * ms / b['step_ms']:>7.1f}%{n:>8d}{mx:>10.2f}")
+    out.append(f"{'not in any bracket: PyTorch eager ops (cat, add, sum, copies), host gaps':<72}{b['step_ms'] - total:>10.2f}"
+               f"{100 * (b['step_ms'] - total) / b['step_ms']:>7.1f}%")
+    return "\n".join(out) + "\n"
 
 
 def _heap_bytes() -> int:
@@ -263,11 +331,18 @@ def main():
                "last_loss": last_loss}
     ms_per_step = ms / a.steps
     value = 1.0 / (ms_per_step / 1e3)
-    flops = model_flops_per_sample(cfg.num_parameters(), tokens, a.text_len, cfg.num_attention_heads,
-                                   cfg.attention_head_dim, cfg.num_layers + cfg.num_single_layers, not a.no_recompute)
+    fl = lambda rec: model_flops_per_sample(cfg.num_parameters(), tokens, a.text_len, cfg.num_attention_heads,  # noqa: E731
+                                            cfg.attention_head_dim, cfg.num_layers + cfg.num_single_layers, rec,
+                                            attention_recomputed=not cfg.recompute_save_attention)
+    flops, flops_executed = fl(False), fl(not a.no_recompute)
+    breakdown = None
+    if a.breakdown:
+        breakdown = run_breakdown(lambda: train_step(fwd_device, None, model, optimizer, scheduler, args), dev)
     if rank == 0:
         from teletron_b200.ops import attention_backend as attn_mod
         from teletron_b200.ops import gemm as gemm_mod
+        from teletron_b200.ops import attn_backward as attn_bwd_mod
+        from teletron_b200.ops import fused_comm as fc_mod
         out = {"metric": "HunyuanVideo-13B 720P train samples/s", "value": value, "unit": "samples/s",
                "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
@@ -280,13 +355,19 @@ def main():
                           "optimizer_state": "split16 master + bf16 moments" if single else "fp32 master + fp32 moments",
                           "l2": "inputs larger than L2: >25 GB of weights and >10 GB of activations stream through every step"},
                "s_per_step": ms_per_step / 1e3, "frames_per_s": value * a.frames,
-               "model_tflops_per_gpu": flops * value / a.gpus / 1e12, "clocks": clocks, "e2e": e2e,
+               # useful = forward + backward of the model; executed adds what the recompute pass really runs again
+               "model_tflops_per_gpu": flops * value / a.gpus / 1e12,
+               "executed_tflops_per_gpu": flops_executed * value / a.gpus / 1e12, "clocks": clocks, "e2e": e2e,
                "gpu_launches": launches,
-               "kernel_backends": {"gemm": dict(gemm_mod.COUNTERS), "attention": dict(attn_mod.COUNTERS)},
+               "kernel_backends": {"gemm": dict(gemm_mod.COUNTERS), "attention": dict(attn_mod.COUNTERS),
+                                   "attention_backward": dict(attn_bwd_mod.COUNTERS), "fused_collective": dict(fc_mod.COUNTERS)},
                # the symmetric heaps (parameter / gradient buffers and collective workspaces of the fused-collective mode)
                # are raw device allocations that the PyTorch allocator's peak does not see
                "peak_mem_gb": (torch.cuda.max_memory_allocated() + _heap_bytes()) / 2 ** 30,
                "peak_mem_torch_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
+        if breakdown is not None:
+            with open(a.breakdown, "w") as fh:
+                fh.write(format_breakdown(breakdown, out))
         print(json.dumps(out), flush=True)
     if dist.is_initialized():
         dist.barrier()

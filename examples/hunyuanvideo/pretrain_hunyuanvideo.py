@@ -65,7 +65,7 @@ def model_provider():
     args.flops_per_sample = model_flops_per_sample(cfg.num_parameters(), tokens, args.text_len,
                                                    cfg.num_attention_heads, cfg.attention_head_dim,
                                                    cfg.num_layers + cfg.num_single_layers,
-                                                   args.recompute_granularity == "full")
+                                                   False)        # useful FLOPs: what an MFU is quoted on
     return pipe
 
 

@@ -346,7 +346,17 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
             const int n0_tile = n0;
             if (EPI == 5) {
               // ---- fused QKV epilogue: every 128 columns of the tile are one head's q, k or v ----
-              // (256-wide tiles keep the tensor core at N = 256; the epilogue walks the two heads one after the other)
+              // (256-wide tiles keep the tensor core at N = 256; the epilogue walks the two heads one after the other.)
+              // Phase 1, one lane per row: accumulator + bias, rounded to bf16 (the value a separate QKV GEMM would hand to
+              // the norm, and the one the backward rebuilds from), into this warp's staging block; 16-byte chunks are
+              // XOR-swizzled by row so that neither phase has more than 2-way bank conflicts.
+              // Phase 2, sixteen lanes per row, two rows per pass: everything that touches global or peer memory is now a
+              // whole 256-byte row per half-warp - the raw copy kept for the backward, the cos / sin tables, and the
+              // store into the owner rank's [head, token, 128] buffer (small scattered stores reach a peer GPU as small
+              // NVLink packets).  RMSNorm sums run over the 16 lanes of a row; bias and norm weights are per-lane constants.
+              const uint32_t sst = epi_stage + (uint32_t)(warp - 2) * 8192u;
+              const int row_base = m0 + quad * 32;
+              const int j = lane & 15, half = lane >> 4;
 #pragma unroll 1
               for (int hh = 0; hh < BN / 128; ++hh) {
                 const int n0 = n0_tile + hh * 128;
@@ -355,7 +365,6 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                 const int idx = n0 / 128;
                 const int head = idx / 3, which = idx - head * 3;
                 const int dest = head / p.heads_per_rank, hl = head - dest * p.heads_per_rank;
-                float v[128];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -363,42 +372,55 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                     tmem_ld_wait();
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        float bv[8];
+                        float bv[8], o[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+                        for (int i = 0; i < 8; ++i) bv[i] = 0.f;
                         if (p.bias != nullptr) tt::unpack8(tt::ld8(p.bias + n0 + c * 32 + g * 8), bv);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[c * 32 + g * 8 + j] = __uint_as_float(r[g * 8 + j]) + bv[j];
+                        for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[g * 8 + i]) + bv[i];
+                        const tt::bf16x8 pk = tt::pack8(o);
+                        const uint4 u = *reinterpret_cast<const uint4*>(&pk);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sst + lane * 256u + (uint32_t)(((c * 4 + g) ^ (lane & 15)) << 4)),
+                                     "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                                     : "memory");
                     }
                 }
-                // the raw projection is kept for every head (the backward rebuilds all of them, also for replicated tokens)
-                if (row_ok && p.aux != nullptr) {
-                    __nv_bfloat16* arow = p.aux + (long)row * p.ldc + n0;
+                __syncwarp();
+                float wv[8];
 #pragma unroll
-                    for (int g = 0; g < 16; ++g) tt::st8(arow + g * 8, tt::pack8(v + g * 8));
-                }
-                const bool keep = row_ok && (!p.only_local || dest == p.my_rank);
-                __nv_bfloat16* drow = nullptr;
-                if (keep) {
+                for (int i = 0; i < 8; ++i) wv[i] = 1.f;
+                if (which < 2) tt::unpack8(tt::ld8((which == 0 ? p.qw : p.kw) + j * 8), wv);
+                __nv_bfloat16* dbase = which == 0 ? p.peer_q[dest] : (which == 1 ? p.peer_k[dest] : p.peer_v[dest]);
+                const bool head_kept = !p.only_local || dest == p.my_rank;
+#pragma unroll 2
+                for (int t = 0; t < 16; ++t) {
+                    const int r = 2 * t + half;
+                    const int row = row_base + r;
+                    const bool ok = row < p.M;
+                    uint4 u;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                                 : "r"(sst + r * 256u + (uint32_t)((j ^ (r & 15)) << 4))
+                                 : "memory");
+                    // the raw projection is kept for every head (the backward rebuilds all of them, also for replicated tokens)
+                    if (ok && p.aux != nullptr) *reinterpret_cast<uint4*>(p.aux + (long)row * p.ldc + n0 + j * 8) = u;
+                    float v[8];
+                    tt::unpack8(*reinterpret_cast<const tt::bf16x8*>(&u), v);
                     const int b = row / p.s_in, srow = row - b * p.s_in;
                     if (which < 2) {
                         float ss = 0.f;
 #pragma unroll
-                        for (int j = 0; j < 128; ++j) ss += v[j] * v[j];
+                        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // the row's 16 lanes
                         const float rstd = rsqrtf(ss * (1.f / 128.f) + p.eps);
-                        const __nv_bfloat16* w = which == 0 ? p.qw : p.kw;
 #pragma unroll
-                        for (int g = 0; g < 16; ++g) {
-                            float wv[8];
-                            tt::unpack8(tt::ld8(w + g * 8), wv);
+                        for (int i = 0; i < 8; ++i) v[i] *= rstd * wv[i];
+                        if (ok && srow < p.rope_len) {
+                            const float4* c4 = reinterpret_cast<const float4*>(p.cos_t + (long)srow * 128 + j * 8);
+                            const float4* s4 = reinterpret_cast<const float4*>(p.sin_t + (long)srow * 128 + j * 8);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) v[g * 8 + j] *= rstd * wv[j];
-                        }
-                        if (srow < p.rope_len) {
-                            const float4* c4 = reinterpret_cast<const float4*>(p.cos_t + (long)srow * 128);
-                            const float4* s4 = reinterpret_cast<const float4*>(p.sin_t + (long)srow * 128);
-#pragma unroll
-                            for (int g = 0; g < 32; ++g) {
+                            for (int g = 0; g < 2; ++g) {
                                 const float4 cc = c4[g], sn = s4[g];
                                 const float a0 = v[4 * g], a1 = v[4 * g + 1], a2 = v[4 * g + 2], a3 = v[4 * g + 3];
                                 v[4 * g] = a0 * cc.x - a1 * sn.x;
@@ -408,21 +430,12 @@ gemm_kernel(const __grid_constant__ TmapArray tmA, const __grid_constant__ CUten
                             }
                         }
                     }
-                    __nv_bfloat16* dbase = which == 0 ? p.peer_q[dest] : (which == 1 ? p.peer_k[dest] : p.peer_v[dest]);
-                    drow = dbase + (((long)b * p.heads_per_rank + hl) * p.s_out + p.out_off + srow) * 128;
-                }
-                if (!p.coalesce) {
-                    if (keep) {
-#pragma unroll
-                        for (int g = 0; g < 16; ++g) tt::st8(drow + g * 8, tt::pack8(v + g * 8));
+                    if (ok && head_kept) {
+                        __nv_bfloat16* drow = dbase + (((long)b * p.heads_per_rank + hl) * p.s_out + p.out_off + srow) * 128;
+                        tt::st8(drow + j * 8, tt::pack8(v));
                     }
-                } else {
-                    // One thread per row stores 16 bytes per instruction: 32 scattered 16-byte writes, which reach a peer GPU
-                    // as 32 small NVLink packets.  Instead the warp's 32 x 128 block goes through shared memory (16-byte
-                    // chunks XOR-swizzled by row, so neither side has more than 2-way bank conflicts) and every store
-                    // instruction then covers two whole 256-byte rows.
-                    store_block_coalesced(v, drow, 128);
                 }
+                __syncwarp();       // the staging block is reused by the next head
               }
             } else {
                 // where this tile's rows land: local C, the owner rank of a column block, or an owner's staging slot
@@ -533,7 +546,7 @@ int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, in
     using C = Cfg<BN>;
     auto kern = gemm_kernel<BN, A_MN, B_MN, EPI, STAGE>;
     // staging for the coalesced peer stores (4 epilogue warps x 8 KB), only when that variant is selected
-    const bool staged_stores = EPI == 6 || (EPI == 5 && p.coalesce);
+    const bool staged_stores = EPI == 6 || EPI == 5;
     const int smem = C::kSmemBytes + (staged_stores ? 4 * 8192 : 0);
     static int configured = 0;
     if (configured < smem) {
@@ -906,7 +919,6 @@ extern "C" int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias,
     p.s_out = s_out;
     p.out_off = out_off;
     p.only_local = only_local;
-    p.coalesce = coalesced_peer_stores();
     for (int r = 0; r < n; ++r) {
         p.peer_q[r] = (__nv_bfloat16*)q_ptrs[r];
         p.peer_k[r] = (__nv_bfloat16*)k_ptrs[r];

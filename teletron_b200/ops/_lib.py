@@ -100,11 +100,59 @@ KERNELS_PER_CALL = {"tt_ln_mod_bwd": 2, "tt_gate_residual_bwd": 2, "tt_rmsnorm_b
 LAUNCHES = 0
 
 
+# Per-phase device time: when switched on, every native call (and every ``phase`` block, used around NCCL collectives and
+# optimizer / gradient-sync sections) is bracketed by two CUDA events on the current stream.  Off, it costs one ``is None`` test.
+_PROFILE: Optional[dict] = None
+
+
+def profile_start() -> None:
+    global _PROFILE
+    _PROFILE = {}
+
+
+def profile_stop() -> dict:
+    """Synchronise and return ``{name: (milliseconds, count)}`` collected since :func:`profile_start`."""
+    global _PROFILE
+    prof, _PROFILE = _PROFILE or {}, None
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    return {k: (sum(a.elapsed_time(b) for a, b in v), len(v)) for k, v in prof.items()}
+
+
+def profiling() -> bool:
+    return _PROFILE is not None
+
+
+class phase:
+    """``with phase("tp all-reduce"): ...`` - device time of the enclosed work on the current stream, when profiling."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.e0 = None
+
+    def __enter__(self):
+        if _PROFILE is not None and torch.cuda.is_available():
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.e0 is not None and _PROFILE is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _PROFILE.setdefault(self.name, []).append((self.e0, e1))
+        return False
+
+
 def call(fn_name: str, *args) -> None:
     """Invoke ``tt_<fn_name>`` and raise on a non-zero status."""
     global LAUNCHES
     fn = getattr(lib(), fn_name)
-    rc = fn(*args)
+    if _PROFILE is not None:
+        with phase(fn_name):
+            rc = fn(*args)
+    else:
+        rc = fn(*args)
     LAUNCHES += KERNELS_PER_CALL.get(fn_name, 1)
     if rc != 0:
         detail = ERRORS.get(rc, "unknown error")

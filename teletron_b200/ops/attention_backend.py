@@ -46,4 +46,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_valid_len: O
             return attn_tcgen05.attention(q, k, v, kv_valid_len, scale)
         if _BACKEND == "tcgen05":
             raise RuntimeError(f"tcgen05 attention does not take q {tuple(q.shape)}")
+        if q.is_cuda and q.dtype == torch.bfloat16:
+            from . import fallback
+            fallback.note("attention", f"q {tuple(q.shape)} {q.dtype}")
     return _sdpa(q, k, v, kv_valid_len, scale)

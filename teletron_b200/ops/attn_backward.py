@@ -16,6 +16,11 @@ _BACKEND = os.environ.get("TELETRON_B200_ATTN_BWD", "auto")
 COUNTERS = {"tcgen05": 0, "flash": 0, "recompute": 0}
 
 
+def _library_fallback(what: str, t: torch.Tensor) -> None:
+    from . import fallback
+    fallback.note(what, f"q {tuple(t.shape)} {t.dtype}")
+
+
 def _flash(dout, q, k, v, out, lse, scale):
     from flash_attn.flash_attn_interface import _flash_attn_backward
     B, H, S, D = q.shape
@@ -35,17 +40,26 @@ def _recompute(dout, q, k, v, scale, kv_len):
         return torch.autograd.grad(o, (qq, kk, vv), dout)
 
 
-def backward(dout, q, k, v, out, lse, scale: float, kv_len: int):
+def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None):
+    """``outs``: optional ``(dq, dk, dv)`` destinations (only the tcgen05 kernel writes in place; the library fallbacks
+    copy into them)."""
     S = q.shape[2]
     if _BACKEND in ("auto", "tcgen05"):
         from . import attn_bwd_tcgen05
         if attn_bwd_tcgen05.supported(q):
             COUNTERS["tcgen05"] += 1
-            return attn_bwd_tcgen05.backward(dout, q, k, v, out, lse, scale, kv_len)
+            return attn_bwd_tcgen05.backward(dout, q, k, v, out, lse, scale, kv_len, outs)
         if _BACKEND == "tcgen05":
             raise RuntimeError("tcgen05 attention backward unavailable")
+    _library_fallback("attention backward", q)
     if kv_len < S:
         COUNTERS["recompute"] += 1
-        return _recompute(dout, q, k, v, scale, kv_len)
-    COUNTERS["flash"] += 1
-    return _flash(dout, q, k, v, out, lse, scale)
+        res = _recompute(dout, q, k, v, scale, kv_len)
+    else:
+        COUNTERS["flash"] += 1
+        res = _flash(dout, q, k, v, out, lse, scale)
+    if outs is not None:
+        for dst, src in zip(outs, res):
+            dst.copy_(src)
+        return tuple(outs)
+    return res

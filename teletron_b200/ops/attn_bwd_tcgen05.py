@@ -16,13 +16,20 @@ def supported(q: torch.Tensor) -> bool:
     return _lib.available() and q.is_cuda and q.dtype == BF16 and q.dim() == 4 and q.shape[-1] == 128
 
 
-def backward(dout, q, k, v, out, lse, scale: float, kv_len: int):
+def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None):
+    """``outs``: optional ``(dq, dk, dv)`` tensors to write into (contiguous, shaped like ``q``), e.g. regions of a
+    symmetric heap that peers will read."""
     B, H, S, D = q.shape
     pitch = lse.shape[-1]
     dout = check(dout.contiguous(), BF16, "dout")
     out = check(out, BF16, "out")
     delta = torch.zeros(B, H, pitch, dtype=torch.float32, device=q.device)
-    dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    if outs is None:
+        dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    else:
+        dq, dk, dv = (check(t, BF16, n) for t, n in zip(outs, ("dq", "dk", "dv")))
+        if any(t.shape != q.shape for t in (dq, dk, dv)):
+            raise _lib.NativeError("gradient outputs must have the shape of q")
     call("tt_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(lse), ptr(delta), ptr(dq), ptr(dk), ptr(dv),
          c_int(B), c_int(H), c_int(S), c_int(kv_len), c_int(pitch), c_float(scale), ptr(status_tensor(q.device)), stream())
     return dq, dk, dv

@@ -159,10 +159,13 @@ class _FusedQKVAllToAll(torch.autograd.Function):
         ws: UlyssesWorkspace = ctx.ws
         x2, xt2, aux, auxt, cosf, sinf, w, qw, kw, wt, qwt, kwt = ctx.saved_tensors
         s, T = ws.s, ws.T
-        ws.heap.barrier()          # previous readers of the gradient buffers are done
-        for name, g in (("dq", dq), ("dk", dk), ("dv", dv)):
-            dst = ws.head_major(name)
-            if g.data_ptr() != dst.data_ptr():
+        pending = [(ws.head_major(name), g) for name, g in (("dq", dq), ("dk", dk), ("dv", dv))
+                   if g.data_ptr() != ws.head_major(name).data_ptr()]
+        if pending:
+            # gradients that were not produced inside the workspace (every rank takes the same branch: it depends on
+            # the producer op only)
+            ws.heap.barrier()      # previous readers of the gradient buffers are done
+            for dst, g in pending:
                 dst.copy_(g)
         ws.heap.barrier()          # every rank's head-sharded gradients are in place
         outs = []
@@ -394,7 +397,10 @@ class _FusedAttentionOutProj(torch.autograd.Function):
         do_local[0, ws.text_off:ws.text_off + T, :].copy_(dot_full[:, ws.rank * span:(ws.rank + 1) * span] * float(ws.cp))
         dext = dot_full[:, G:].contiguous().view(ctx.extra_shapes[1]) if ext is not None else None
         ws.heap.barrier()                  # all pushed gradient tiles have landed
-        dq, dk, dv = attn_backward.backward(do_local, q, k, v, out, lse, ctx.sc, ctx.kvl)
+        # dq / dk / dv are written straight into the workspace regions that the peers read in the QKV backward.  Their
+        # last readers (the peers' QKV backward of the layer above) finished before the two barriers of this function.
+        dq, dk, dv = attn_backward.backward(do_local, q, k, v, out, lse, ctx.sc, ctx.kvl,
+                                            outs=tuple(ws.head_major(n) for n in ("dq", "dk", "dv")))
         del dwt_same
         return (None, None, None, None, dq, dk, dv, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
 

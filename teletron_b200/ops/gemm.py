@@ -41,6 +41,9 @@ def _native(a: torch.Tensor, b: torch.Tensor, layout: str, bias: Optional[torch.
     if not gemm_tcgen05.supported(a, b, layout):
         if _BACKEND == "tcgen05":
             raise RuntimeError(f"tcgen05 GEMM does not take {layout} {tuple(a.shape)} x {tuple(b.shape)}")
+        if a.is_cuda and a.dtype == torch.bfloat16:
+            from . import fallback
+            fallback.note("gemm", f"{layout} {tuple(a.shape)} x {tuple(b.shape)} strides {a.stride()} {b.stride()}")
         return None
     COUNTERS["tcgen05"] += 1
     return gemm_tcgen05.gemm(a, b, layout, bias)
@@ -78,6 +81,9 @@ def gemm_tn_into(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.T
             COUNTERS["tcgen05"] += 1
             gemm_tcgen05.gemm(a, b, "tn", out=out)
             return out
+    if _BACKEND != "cublas" and a.is_cuda and a.dtype == torch.bfloat16:
+        from . import fallback
+        fallback.note("gemm", f"tn-into {tuple(a.shape)} x {tuple(b.shape)} out strides {out.stride()}")
     COUNTERS["cublas"] += 1
-    out.copy_(torch.matmul(a.t(), b))
+    torch.matmul(a.t(), b, out=out) if out.is_contiguous() else out.copy_(torch.matmul(a.t(), b))
     return out

@@ -258,12 +258,14 @@ class DistributedDataParallel(nn.Module):
             FC.fused_grad_reduce_scatter(self.heap, self.heap_offsets[1], s, e - s, buf.grad_data[s:e], self.grad_scale)
             b.handle = "fused"
             return
-        g.mul_(self.grad_scale)
-        if self.use_distributed_optimizer:
-            s, e = buf.shard_range(b, self.rank)
-            b.handle = dist.reduce_scatter_tensor(buf.grad_data[s:e], g, group=self.group, async_op=async_op)
-        else:
-            b.handle = dist.all_reduce(g, group=self.group, async_op=async_op)
+        from ..ops import _lib
+        with _lib.phase("nccl gradient reduce"):
+            g.mul_(self.grad_scale)
+            if self.use_distributed_optimizer:
+                s, e = buf.shard_range(b, self.rank)
+                b.handle = dist.reduce_scatter_tensor(buf.grad_data[s:e], g, group=self.group, async_op=async_op)
+            else:
+                b.handle = dist.all_reduce(g, group=self.group, async_op=async_op)
 
     def start_grad_sync(self):
         for buf in self.buffers:

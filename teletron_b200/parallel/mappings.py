@@ -18,6 +18,11 @@ import torch
 import torch.distributed as dist
 
 
+def _phase(name: str):
+    from ..ops import _lib
+    return _lib.phase(name)
+
+
 def _size(group) -> int:
     return 1 if group is None else dist.get_world_size(group)
 
@@ -193,15 +198,22 @@ class _CopyToTP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous()
-        dist.all_reduce(g, group=ctx.group)
+        with _phase("nccl tp all-reduce (bwd)"):
+            dist.all_reduce(g, group=ctx.group)
         return g, None
 
 
 class _ReduceFromTP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
-        x = x.contiguous().clone()
-        dist.all_reduce(x, group=group)
+        # reduced in place when the partial product is a dense tensor of its own (the usual case: a fresh GEMM output);
+        # no copy of the activation is made
+        if x.is_contiguous() and x._base is None and not x.is_leaf:
+            ctx.mark_dirty(x)
+        else:
+            x = x.contiguous().clone()
+        with _phase("nccl tp all-reduce (fwd)"):
+            dist.all_reduce(x, group=group)
         return x
 
     @staticmethod

@@ -83,6 +83,9 @@ def _add_parallel_args(p):
                    help="pad every context-parallel chunk of video tokens to a multiple of this (keeps weight-gradient GEMMs on the tensor-core kernel)")
     g.add_argument("--sequence-parallel", action="store_true",
                    help="shard activations over TP between GEMMs (all-gather->GEMM / GEMM->reduce-scatter)")
+    g.add_argument("--allow-library-fallback", action="store_true",
+                   help="let GEMM / attention cases that the sm_100a kernels do not take run on cuBLAS / SDPA (logged once per "
+                        "shape) instead of raising")
     g.add_argument("--fused-comm", action="store_true",
                    help="use the in-kernel NVLink collectives (fused Ulysses all-to-all, AG-GEMM, GEMM-RS)")
     g.add_argument("--comm-barrier-timeout-seconds", type=float, default=10.0,

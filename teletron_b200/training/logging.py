@@ -134,17 +134,17 @@ class Timers:
 
 
 def model_flops_per_sample(num_params_blocks: int, video_tokens: int, text_tokens: int, heads: int, head_dim: int,
-                           n_blocks: int, recompute: bool) -> float:
-    """Model FLOPs of one training sample: linears ``2 * P * tokens`` and attention
-    ``4 * tokens^2 * head_dim * heads`` per block forward; backward = 2x forward (attention
-    backward 2.5x); full recompute adds one more forward."""
+                           n_blocks: int, recompute: bool, attention_recomputed: bool = True) -> float:
+    """FLOPs executed for one training sample: linears ``2 * P * tokens`` and attention
+    ``4 * tokens^2 * head_dim * heads`` per block forward; backward = 2x forward (attention backward 2.5x); full
+    recompute adds one more forward of the linears, and of attention too unless the attention output is kept
+    (``attention_recomputed=False``).  ``recompute=False`` gives the useful (model) FLOPs that an MFU is quoted on."""
     n = video_tokens + text_tokens
     lin = 2.0 * num_params_blocks * n
     att = 4.0 * n * n * head_dim * heads * n_blocks
-    fwd = lin + att
-    total = fwd + 2.0 * lin + 2.5 * att
+    total = 3.0 * lin + 3.5 * att
     if recompute:
-        total += fwd
+        total += lin + (att if attention_recomputed else 0.0)
     return total
 
 

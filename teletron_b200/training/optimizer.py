@@ -140,9 +140,11 @@ class DistributedOptimizer:
                     FC.fused_param_all_gather(self.ddp.heap, self.ddp.heap_offsets[0], st.start, buf.param_data[st.start:st.end])
                 self.ddp.heap.barrier()
             elif self.sharded:
-                for b, st in zip(buf.buckets, states):
-                    dist.all_gather_into_tensor(buf.param_data[b.start:b.end], buf.param_data[st.start:st.end],
-                                                group=self.ddp.group)
+                from ..ops import _lib
+                with _lib.phase("nccl parameter all-gather"):
+                    for b, st in zip(buf.buckets, states):
+                        dist.all_gather_into_tensor(buf.param_data[b.start:b.end], buf.param_data[st.start:st.end],
+                                                    group=self.ddp.group)
         return True
 
     def zero_grad(self, set_to_none: bool = False):

@@ -88,6 +88,9 @@ def initialize(extra_args_provider: Optional[Callable] = None, argv=None, args_d
                                  timeout_minutes=args.distributed_timeout_minutes)
     if ps.is_dit_rank():
         set_random_seed(args.seed, args.data_parallel_random_init)
+    if use_cuda:
+        from ..ops import fallback
+        fallback.set_strict(not args.allow_library_fallback)
     if args.fused_comm:
         from ..models.hunyuanvideo import blocks
         from ..parallel import symm_mem
