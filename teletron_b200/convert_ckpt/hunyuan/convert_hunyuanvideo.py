@@ -21,8 +21,10 @@ from __future__ import annotations
 
 import argparse
 import glob
+import json
 import os
 import re
+import shutil
 from types import SimpleNamespace
 from typing import Dict, List, Optional
 
@@ -223,12 +225,90 @@ def convert_hf_to_tel(load_path: str, save_path: str, tp: int, dtype: torch.dtyp
     save_tel_checkpoint(save_path, shard_state(full, tp, hidden, mlp_hidden), dtype, vae)
 
 
+def _parse_size(text: str) -> int:
+    t = text.strip().upper()
+    for suffix, mult in (("GIB", 2 ** 30), ("MIB", 2 ** 20), ("KIB", 2 ** 10), ("GB", 10 ** 9), ("MB", 10 ** 6), ("KB", 10 ** 3)):
+        if t.endswith(suffix):
+            return int(float(t[:-len(suffix)]) * mult)
+    return int(t)
+
+
+def hf_transformer_config(hf: Dict[str, torch.Tensor], heads: int, hidden: int) -> dict:
+    """``config.json`` of a diffusers ``HunyuanVideoTransformer3DModel`` derived from the weights themselves (used when the
+    checkpoint being converted back has no original ``config.json`` next to it)."""
+    import re
+    n_dual = 1 + max((int(m.group(1)) for k in hf for m in [re.match(r"transformer_blocks\.(\d+)\.", k)] if m), default=-1)
+    n_single = 1 + max((int(m.group(1)) for k in hf for m in [re.match(r"single_transformer_blocks\.(\d+)\.", k)] if m), default=-1)
+    n_ref = 1 + max((int(m.group(1)) for k in hf for m in [re.match(r"context_embedder\.token_refiner\.refiner_blocks\.(\d+)\.", k)] if m),
+                    default=-1)
+    cfg = {"_class_name": "HunyuanVideoTransformer3DModel", "num_attention_heads": heads, "attention_head_dim": hidden // heads,
+           "num_layers": n_dual, "num_single_layers": n_single, "num_refiner_layers": n_ref, "mlp_ratio": 4.0, "patch_size": 2,
+           "patch_size_t": 1, "qk_norm": "rms_norm", "guidance_embeds": any(k.startswith("time_text_embed.guidance_embedder") for k in hf),
+           "rope_axes_dim": [16, 56, 56], "rope_theta": 256.0}
+    w = hf.get("x_embedder.proj.weight")
+    if w is not None:
+        cfg["in_channels"] = int(w.shape[1])
+    w = hf.get("proj_out.weight")
+    if w is not None:
+        cfg["out_channels"] = int(w.shape[0]) // 4          # patch 1 x 2 x 2
+    w = hf.get("context_embedder.proj_in.weight")
+    if w is not None:
+        cfg["text_embed_dim"] = int(w.shape[1])
+    w = hf.get("time_text_embed.text_embedder.linear_1.weight")
+    if w is not None:
+        cfg["pooled_projection_dim"] = int(w.shape[1])
+    return cfg
+
+
+def save_hf_sharded(hf: Dict[str, torch.Tensor], save_path: str, max_shard_size: str = "10GB",
+                    config: Optional[dict] = None, config_from: Optional[str] = None) -> List[str]:
+    """Write a diffusers-loadable transformer folder: ``diffusion_pytorch_model.safetensors`` (one shard) or
+    ``diffusion_pytorch_model-0000x-of-0000y.safetensors`` + ``diffusion_pytorch_model.safetensors.index.json``, and
+    ``config.json``.  The reference writes ``.bin`` shards, the same index name and copies the original config
+    (``convert_hunyuanvideo.py:980-1006``); safetensors is what current diffusers looks for first."""
+    from safetensors.torch import save_file
+    os.makedirs(save_path, exist_ok=True)
+    limit = _parse_size(max_shard_size)
+    shards, cur, cur_bytes = [], {}, 0
+    for k, v in hf.items():                                     # key order kept: blocks stay together in a shard
+        nb = v.numel() * v.element_size()
+        if cur and cur_bytes + nb > limit:
+            shards.append(cur)
+            cur, cur_bytes = {}, 0
+        cur[k] = v.contiguous()
+        cur_bytes += nb
+    if cur:
+        shards.append(cur)
+    names = []
+    if len(shards) == 1:
+        names.append("diffusion_pytorch_model.safetensors")
+        save_file(shards[0], os.path.join(save_path, names[0]), metadata={"format": "pt"})
+    else:
+        weight_map = {}
+        for i, sh in enumerate(shards):
+            name = f"diffusion_pytorch_model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+            names.append(name)
+            save_file(sh, os.path.join(save_path, name), metadata={"format": "pt"})
+            weight_map.update({k: name for k in sh})
+        total = sum(v.numel() * v.element_size() for v in hf.values())
+        with open(os.path.join(save_path, "diffusion_pytorch_model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=2)
+    src = os.path.join(config_from, "config.json") if config_from else None
+    if src and os.path.isfile(src):
+        shutil.copyfile(src, os.path.join(save_path, "config.json"))
+    elif config is not None:
+        with open(os.path.join(save_path, "config.json"), "w") as f:
+            json.dump(config, f, indent=2)
+    return names
+
+
 def convert_tel_to_hf(load_path: str, save_path: str, dtype: torch.dtype, heads: int = 24, hidden: int = 3072,
-                      mlp_hidden: int = 12288) -> None:
+                      mlp_hidden: int = 12288, max_shard_size: str = "10GB") -> None:
     full = merge_shards(load_tel_checkpoint(load_path), hidden, mlp_hidden)
     hf = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tel_to_hf_state(full, heads).items()}
-    os.makedirs(save_path, exist_ok=True)
-    torch.save(hf, os.path.join(save_path, "diffusion_pytorch_model.pt"))
+    # the original diffusers config, if the TeleTron checkpoint sits next to one (as the reference assumes), else derived
+    save_hf_sharded(hf, save_path, max_shard_size, config=hf_transformer_config(hf, heads, hidden),
+                    config_from=os.path.dirname(os.path.abspath(load_path.rstrip("/"))))
 
 
 def get_args(argv=None):
@@ -243,6 +323,7 @@ def get_args(argv=None):
     p.add_argument("--num-attention-heads", type=int, default=24)
     p.add_argument("--hidden-size", type=int, default=3072)
     p.add_argument("--mlp-hidden-size", type=int, default=12288)
+    p.add_argument("--max-shard-size", type=str, default="10GB", help="TeleTron -> HF: largest safetensors shard (e.g. 5GB, 42GB)")
     return p.parse_args(argv)
 
 
@@ -252,7 +333,8 @@ def main(argv=None):
         raise SystemExit("pipeline parallelism is not supported by the HunyuanVideo model (every rank owns all blocks)")
     dtype = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[a.target_params_dtype]
     if a.convert_checkpoint_from_megatron_to_transformers:
-        convert_tel_to_hf(a.load_path, a.save_path, dtype, a.num_attention_heads, a.hidden_size, a.mlp_hidden_size)
+        convert_tel_to_hf(a.load_path, a.save_path, dtype, a.num_attention_heads, a.hidden_size, a.mlp_hidden_size,
+                          a.max_shard_size)
     else:
         vae = os.path.join(a.hf_ckpt_path, "vae") if a.hf_ckpt_path and os.path.isdir(os.path.join(a.hf_ckpt_path, "vae")) else None
         convert_hf_to_tel(a.load_path, a.save_path, a.target_tensor_model_parallel_size, dtype, a.num_attention_heads,

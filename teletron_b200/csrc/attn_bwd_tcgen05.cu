@@ -58,6 +58,7 @@ struct BwdParams {
     const float* lse;       // [BH, pitch]; entries at and beyond S hold +inf
     const float* delta;     // [BH, pitch]; entries at and beyond S hold 0
     int S, kv_len, H;
+    int mask_lo, mask_hi;   // keys in [mask_lo, mask_hi) are masked in addition to those at and beyond kv_len
     int pitch;              // multiple of 64, so every 64-query chunk of statistics is 16-byte aligned
     float scale;            // softmax scale
     int* status;
@@ -267,7 +268,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         float my_lse = 0.f, my_delta = 0.f;
         bool row_live;
         if (KVS) {
-            row_live = row < p.kv_len;
+            row_live = row < p.kv_len && !(row >= p.mask_lo && row < p.mask_hi);
         } else {
             row_live = row < p.S;
             my_lse = row_live ? p.lse[(long)bh * p.pitch + row] * kLog2e : INFINITY;
@@ -337,8 +338,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                         if (!row_live) pr = make_float2(0.f, 0.f);
                     } else {
                         const int cc = col0 + pass * 32 + 2 * i;
-                        if (cc >= p.kv_len) pr.x = 0.f;
-                        if (cc + 1 >= p.kv_len) pr.y = 0.f;
+                        if (cc >= p.kv_len || (cc >= p.mask_lo && cc < p.mask_hi)) pr.x = 0.f;
+                        if (cc + 1 >= p.kv_len || (cc + 1 >= p.mask_lo && cc + 1 < p.mask_hi)) pr.y = 0.f;
                     }
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(pr.x, pr.y);
                     pk[pass * 16 + i] = *reinterpret_cast<const uint32_t*>(&pb);
@@ -435,8 +436,9 @@ done:
 // (delta is scratch owned by the caller, zero-initialised; this call fills positions < S).
 extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                            const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len,
-                           int pitch, float scale, int* status, void* stream) {
+                           int mask_lo, int mask_hi, int pitch, float scale, int* status, void* stream) {
     if (B <= 0 || H <= 0 || S <= 0 || kv_len <= 0 || kv_len > S || status == nullptr || delta == nullptr) return TT_ERR_ARG;
+    if (mask_lo < mask_hi && (mask_lo < 0 || (mask_lo == 0 && mask_hi >= kv_len))) return TT_ERR_ARG;
     if (pitch < S || (pitch & 63) || ((uintptr_t)lse & 15) || ((uintptr_t)delta & 15)) return TT_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const uint64_t BH = (uint64_t)B * H;
@@ -466,6 +468,8 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     p.delta = delta;
     p.S = S;
     p.kv_len = kv_len;
+    p.mask_lo = mask_lo;
+    p.mask_hi = mask_lo < mask_hi ? mask_hi : mask_lo;
     p.H = H;
     p.pitch = pitch;
     p.scale = scale;

@@ -45,6 +45,7 @@ struct AttnParams {
     int lse_pitch;
     int S;                // query / key sequence length
     int kv_len;           // keys >= kv_len are masked
+    int mask_lo, mask_hi; // keys in [mask_lo, mask_hi) are masked as well (padded text tokens that are not the sequence tail)
     int H;                // heads (for the output layout)
     float scale_log2;     // softmax scale * log2(e)
     int* status;
@@ -201,7 +202,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!mbar_wait(s_full(t), (uint32_t)j & 1u, &abort_flag)) goto done;
             tc_fence_after();
             const int valid = p.kv_len - j * BKV;      // columns >= valid are masked (only in the last tile)
-            const bool full_tile = valid >= BKV;
+            const int lo = p.mask_lo - j * BKV, hi = p.mask_hi - j * BKV;      // and columns [lo, hi) of this tile
+            const bool full_tile = valid >= BKV && (lo >= hi || hi <= 0 || lo >= BKV);
             // pass 1: row maximum (3-input max, four independent chains)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -212,7 +214,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 if (!full_tile) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i >= valid) r[i] = 0xff800000u;      // -inf
+                        if (c * 32 + i >= valid || (c * 32 + i >= lo && c * 32 + i < hi)) r[i] = 0xff800000u;      // -inf
                 }
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
@@ -256,8 +258,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     float2 e = make_float2(exp2f(x.x), exp2f(x.y));
                     if (!full_tile) {
                         const int c0 = c * 32 + 2 * i;
-                        if (c0 >= valid) e.x = 0.f;
-                        if (c0 + 1 >= valid) e.y = 0.f;
+                        if (c0 >= valid || (c0 >= lo && c0 < hi)) e.x = 0.f;
+                        if (c0 + 1 >= valid || (c0 + 1 >= lo && c0 + 1 < hi)) e.y = 0.f;
                     }
                     if (i & 1) sum2b = __fadd2_rn(sum2b, e);
                     else sum2a = __fadd2_rn(sum2a, e);
@@ -332,12 +334,15 @@ done:
 
 // q, k, v: [BH, S, 128] bf16 contiguous; out [B, S, H*128] bf16; lse [BH, lse_pitch] fp32 (rows < S written).
 static int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
-                           int kv_len, int lse_pitch, float scale, int* status, void* stream, void* const* peer_out,
-                           int n_peers, int my_rank, int text_len, int s_local, long dest_ld);
+                           int kv_len, int mask_lo, int mask_hi, int lse_pitch, float scale, int* status, void* stream,
+                           void* const* peer_out, int n_peers, int my_rank, int text_len, int s_local, long dest_ld);
 
+// Keys at and beyond kv_len are masked, and so are keys in [mask_lo, mask_hi) (pass mask_lo >= mask_hi for none); at least
+// one key must stay visible.
 extern "C" int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
-                           int kv_len, int lse_pitch, float scale, int* status, void* stream) {
-    return attn_fwd_launch(q, k, v, out, lse, B, H, S, kv_len, lse_pitch, scale, status, stream, nullptr, 0, 0, 0, 0, 0);
+                           int kv_len, int mask_lo, int mask_hi, int lse_pitch, float scale, int* status, void* stream) {
+    return attn_fwd_launch(q, k, v, out, lse, B, H, S, kv_len, mask_lo, mask_hi, lse_pitch, scale, status, stream, nullptr,
+                           0, 0, 0, 0, 0);
 }
 
 // Forward with the Ulysses head -> sequence all-to-all fused into the epilogue (batch 1).  The sequence is
@@ -345,18 +350,19 @@ extern "C" int tt_attn_fwd(const void* q, const void* k, const void* v, void* ou
 // [text_len + s_local, dest_ld] (dest_ld = n_peers * H * 128) and receives this rank's H heads at columns
 // [my_rank * H * 128, (my_rank + 1) * H * 128).  `out` still receives the local head-sharded copy for the backward.
 extern "C" int tt_attn_fwd_push(const void* q, const void* k, const void* v, void* out, float* lse, int H, int S,
-                                int kv_len, int lse_pitch, float scale, int* status, void* stream, void* const* peer_out,
-                                int n_peers, int my_rank, int text_len, int s_local, long dest_ld) {
+                                int kv_len, int mask_lo, int mask_hi, int lse_pitch, float scale, int* status, void* stream,
+                                void* const* peer_out, int n_peers, int my_rank, int text_len, int s_local, long dest_ld) {
     if (peer_out == nullptr || n_peers < 1 || n_peers > TT_MAX_PEERS || my_rank < 0 || my_rank >= n_peers) return TT_ERR_ARG;
     if (text_len < 0 || s_local <= 0 || text_len + (long)n_peers * s_local != S || (dest_ld & 7)) return TT_ERR_ARG;
-    return attn_fwd_launch(q, k, v, out, lse, 1, H, S, kv_len, lse_pitch, scale, status, stream, peer_out, n_peers, my_rank,
-                           text_len, s_local, dest_ld);
+    return attn_fwd_launch(q, k, v, out, lse, 1, H, S, kv_len, mask_lo, mask_hi, lse_pitch, scale, status, stream, peer_out,
+                           n_peers, my_rank, text_len, s_local, dest_ld);
 }
 
 static int attn_fwd_launch(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S,
-                           int kv_len, int lse_pitch, float scale, int* status, void* stream, void* const* peer_out,
-                           int n_peers, int my_rank, int text_len, int s_local, long dest_ld) {
+                           int kv_len, int mask_lo, int mask_hi, int lse_pitch, float scale, int* status, void* stream,
+                           void* const* peer_out, int n_peers, int my_rank, int text_len, int s_local, long dest_ld) {
     if (B <= 0 || H <= 0 || S <= 0 || kv_len <= 0 || kv_len > S || lse_pitch < S || status == nullptr) return TT_ERR_ARG;
+    if (mask_lo < mask_hi && (mask_lo < 0 || (mask_lo == 0 && mask_hi >= kv_len))) return TT_ERR_ARG;
     CUtensorMap tq, tk, tv;
     int rc;
     const uint64_t BH = (uint64_t)B * H;
@@ -375,6 +381,8 @@ static int attn_fwd_launch(const void* q, const void* k, const void* v, void* ou
     p.lse_pitch = lse_pitch;
     p.S = S;
     p.kv_len = kv_len;
+    p.mask_lo = mask_lo;
+    p.mask_hi = mask_lo < mask_hi ? mask_hi : mask_lo;
     p.H = H;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;

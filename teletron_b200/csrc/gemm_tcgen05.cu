@@ -664,14 +664,17 @@ void default_params(GemmParams& p) {
     p.n_seg = 1;
 }
 
-// TELETRON_B200_COALESCED_PEER_STORES=1: epilogues that push tiles to a peer stage them in shared memory and store whole
-// 256-byte rows per instruction; off by default
+// Epilogues that push tiles to a peer (column blocks of a data gradient, row blocks of a reduce-scatter) can stage each
+// warp's 32 x 128 block in shared memory and store whole 256-byte rows per instruction instead of 16 bytes per thread
+// and row.  Chosen by tt_set_coalesced_peer_stores(), else by TELETRON_B200_COALESCED_PEER_STORES (default on).
+int g_coalesce = -1;
+
 int coalesced_peer_stores() {
-    static const int on = [] {
+    if (g_coalesce < 0) {
         const char* v = getenv("TELETRON_B200_COALESCED_PEER_STORES");
-        return (v != nullptr && v[0] == '1') ? 1 : 0;
-    }();
-    return on;
+        g_coalesce = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return g_coalesce;
 }
 
 int pick_bn(int M, int N, int sms, bool force128) {
@@ -681,6 +684,8 @@ int pick_bn(int M, int N, int sms, bool force128) {
 }
 
 }  // namespace
+
+extern "C" void tt_set_coalesced_peer_stores(int on) { g_coalesce = on ? 1 : 0; }
 
 // C[M, N] = epilogue(op(A) op(B)^T ...) as described at the top of this file.
 //   a_mn == 0: a is A[M, K] with row pitch lda;   a_mn == 1: a is A^T stored [K, M] with row pitch lda

@@ -61,9 +61,18 @@ int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, voi
              int state_is_bf16, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale,
              void* stream);
 
+/* gradient reduce-scatter + AdamW + parameter all-gather on one shard of flat buffers that live in peer-mapped memory
+ * (grad_ptrs [n_g] sources, param_ptrs [n_p] destinations, this rank's own at my_p; see optim.cu) */
+int tt_rs_adamw_ag(void* const* grad_ptrs, int n_g, void* const* param_ptrs, int n_p, int my_p, long offset, void* m,
+                   void* v, float* master, void* master_lo, long n, int state_is_bf16, float lr, float beta1,
+                   float beta2, float eps, float wd, int step, float grad_scale, void* stream);
+
 /* ---- tcgen05 GEMM (see gemm_tcgen05.cu for the layout / epilogue codes) ---- */
 int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
+
+/* pushed tiles (tt_gemm_comm_bf16 store modes 1 / 2): 1 = staged stores of whole 256-byte rows (default), 0 = 16 bytes per thread */
+void tt_set_coalesced_peer_stores(int on);
 
 /* GEMM fused with a collective over peer memory, and the fused QKV projection (see gemm_tcgen05.cu) */
 int tt_gemm_comm_bf16(void* const* a_ptrs, int n, int a_mode, long a_rows, int a_span, int a_row_off,
@@ -78,14 +87,15 @@ int tt_qkv_gemm_fused(const void* x, const void* w, const void* bias, const void
 
 /* ---- tcgen05 flash attention: q, k, v, dq, dk, dv [B*H, S, 128]; out, dout [B, S, H*128];
  *      lse, delta [B*H, pitch] fp32, pitch % 64 == 0, lse = +inf and delta = 0 at positions >= S ---- */
+/* masked keys: those at and beyond kv_len, and those in [mask_lo, mask_hi) (mask_lo >= mask_hi: no such range) */
 int tt_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int S, int kv_len,
-                int lse_pitch, float scale, int* status, void* stream);
+                int mask_lo, int mask_hi, int lse_pitch, float scale, int* status, void* stream);
 int tt_attn_fwd_push(const void* q, const void* k, const void* v, void* out, float* lse, int H, int S, int kv_len,
-                     int lse_pitch, float scale, int* status, void* stream, void* const* peer_out, int n_peers, int my_rank,
-                     int text_len, int s_local, long dest_ld);
+                     int mask_lo, int mask_hi, int lse_pitch, float scale, int* status, void* stream,
+                     void* const* peer_out, int n_peers, int my_rank, int text_len, int s_local, long dest_ld);
 int tt_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
-                float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len, int pitch, float scale,
-                int* status, void* stream);
+                float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len, int mask_lo, int mask_hi,
+                int pitch, float scale, int* status, void* stream);
 
 /* ---- symmetric heap + in-kernel collectives over IPC-mapped peer memory (comm.cu) ---- */
 int tt_symm_alloc(size_t bytes, void** out);                 /* cudaMalloc + zero */

@@ -301,10 +301,12 @@ def _workspace(heads_local: int, s: int, T: int):
     return _cached_workspace((heads_local, s, T), lambda: UlyssesWorkspace(ps.get_context_parallel_group(), heads_local, s, T))
 
 
-def _fused_kv_len(ws, pad: Optional[SeqPad], kv_valid_len) -> Optional[int]:
-    if kv_valid_len is not None:
-        raise NotImplementedError("the text key mask is not available together with --fused-comm")
-    return None if pad is None or pad.pad == 0 else ws.T + pad.origin
+def _fused_kv_len(ws, pad: Optional[SeqPad], kv_valid_len):
+    """``(kv_len, mask_range)`` for the fused layout ``[text | video of rank 0 | video of rank 1 | ...]``: context-parallel
+    padding is the sequence tail (a key length), padded text tokens ``[kv_valid_len, T)`` are a range of their own."""
+    kv_len = None if pad is None or pad.pad == 0 else ws.T + pad.origin
+    mask = None if kv_valid_len is None or kv_valid_len >= ws.T else (int(kv_valid_len), ws.T)
+    return kv_len, mask
 
 
 class JointAttention(nn.Module):
@@ -358,11 +360,11 @@ class JointAttention(nn.Module):
     def project_fused(self, handle):
         """Attention (its epilogue does the head->seq all-to-all) followed by the two output projections."""
         from ...ops import fused_comm as FC
-        _, ws, (q, k, v), kv_len = handle
+        _, ws, (q, k, v), (kv_len, mask) = handle
         tp = self.linear_proj.tp
         y, yt = FC.fused_attention_outproj(ws, q, k, v, self.linear_proj.weight, self.linear_proj.bias if tp == 1 else None,
                                            self.added_linear_proj.weight, self.added_linear_proj.bias if tp == 1 else None,
-                                           kv_len=kv_len)
+                                           kv_len=kv_len, mask_range=mask)
         if tp > 1:
             y = tp_region_output(y, self.sequence_parallel) + self.linear_proj.bias
             yt = tp_region_output(yt, self.sequence_parallel) + self.added_linear_proj.bias
@@ -487,8 +489,9 @@ class HunyuanSingleDiTLayer(nn.Module):
                                    xt, w, b, sa.q_layernorm.weight, sa.k_layernorm.weight, sa.eps)
         tp = self.proj_out.tp
         wo, bo = self.proj_out.weight, (self.proj_out.bias if tp == 1 else None)
+        kv_len, mask = _fused_kv_len(ws, pad, kv_valid_len)
         y, yt = FC.fused_attention_outproj(ws, q, k, v, wo, bo, wo, bo, extra=mlp[:, :s], extra_t=mlp[:, s:],
-                                           kv_len=_fused_kv_len(ws, pad, kv_valid_len))
+                                           kv_len=kv_len, mask_range=mask)
         proj = torch.cat([y, yt], dim=1)
         if tp > 1:
             proj = tp_region_output(proj, self.sequence_parallel, (s, T) if self.sequence_parallel else None) + self.proj_out.bias

@@ -131,11 +131,12 @@ def linear(x, weight, bias=None, activation=None):
     return reference.linear(x, weight, bias, activation)
 
 
-def attention(q, k, v, kv_valid_len=None, scale=None):
+def attention(q, k, v, kv_valid_len=None, scale=None, mask_range=None):
+    """``kv_valid_len`` masks the key tail, ``mask_range = (lo, hi)`` one more key range."""
     if _use_cuda(q):
         from . import cuda_ops
-        return cuda_ops.attention(q, k, v, kv_valid_len, scale)
-    return reference.attention(q, k, v, kv_valid_len, scale)
+        return cuda_ops.attention(q, k, v, kv_valid_len, scale, mask_range)
+    return reference.attention(q, k, v, kv_valid_len, scale, mask_range)
 
 
 def qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin, num_heads,

@@ -26,27 +26,22 @@ def set_backend(name: str) -> None:
     _BACKEND = name
 
 
-def _sdpa(q, k, v, kv_valid_len, scale):
+def _sdpa(q, k, v, kv_valid_len, scale, mask_range=None):
     COUNTERS["sdpa"] += 1
-    B, h, S, D = q.shape
-    mask = None
-    if kv_valid_len is not None and kv_valid_len < k.shape[2]:
-        mask = torch.zeros(1, 1, 1, k.shape[2], dtype=torch.bool, device=q.device)
-        mask[..., :kv_valid_len] = True
-    o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, scale=scale)
-    return o.transpose(1, 2).reshape(B, S, h * D)
+    from . import reference
+    return reference.attention(q, k, v, kv_valid_len, scale, mask_range)
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_valid_len: Optional[int] = None,
-              scale: Optional[float] = None) -> torch.Tensor:
+              scale: Optional[float] = None, mask_range=None) -> torch.Tensor:
     if _BACKEND != "sdpa":
         from . import attn_tcgen05
         if attn_tcgen05.supported(q, k, v):
             COUNTERS["tcgen05"] += 1
-            return attn_tcgen05.attention(q, k, v, kv_valid_len, scale)
+            return attn_tcgen05.attention(q, k, v, kv_valid_len, scale, mask_range)
         if _BACKEND == "tcgen05":
             raise RuntimeError(f"tcgen05 attention does not take q {tuple(q.shape)}")
         if q.is_cuda and q.dtype == torch.bfloat16:
             from . import fallback
             fallback.note("attention", f"q {tuple(q.shape)} {q.dtype}")
-    return _sdpa(q, k, v, kv_valid_len, scale)
+    return _sdpa(q, k, v, kv_valid_len, scale, mask_range)

@@ -31,16 +31,16 @@ def _flash(dout, q, k, v, out, lse, scale):
     return dq, dk, dv
 
 
-def _recompute(dout, q, k, v, scale, kv_len):
+def _recompute(dout, q, k, v, scale, kv_len, mask_range=None):
     """Reference-grade fallback: differentiate the PyTorch attention (used for masked keys)."""
     from . import reference
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
-        o = reference.attention(qq, kk, vv, kv_len if kv_len < q.shape[2] else None, scale)
+        o = reference.attention(qq, kk, vv, kv_len if kv_len < q.shape[2] else None, scale, mask_range)
         return torch.autograd.grad(o, (qq, kk, vv), dout)
 
 
-def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None):
+def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None, mask_range=(0, 0)):
     """``outs``: optional ``(dq, dk, dv)`` destinations (only the tcgen05 kernel writes in place; the library fallbacks
     copy into them)."""
     S = q.shape[2]
@@ -48,13 +48,13 @@ def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None):
         from . import attn_bwd_tcgen05
         if attn_bwd_tcgen05.supported(q):
             COUNTERS["tcgen05"] += 1
-            return attn_bwd_tcgen05.backward(dout, q, k, v, out, lse, scale, kv_len, outs)
+            return attn_bwd_tcgen05.backward(dout, q, k, v, out, lse, scale, kv_len, outs, mask_range or (0, 0))
         if _BACKEND == "tcgen05":
             raise RuntimeError("tcgen05 attention backward unavailable")
     _library_fallback("attention backward", q)
-    if kv_len < S:
+    if kv_len < S or (mask_range and mask_range[0] < mask_range[1]):
         COUNTERS["recompute"] += 1
-        res = _recompute(dout, q, k, v, scale, kv_len)
+        res = _recompute(dout, q, k, v, scale, kv_len, mask_range)
     else:
         COUNTERS["flash"] += 1
         res = _flash(dout, q, k, v, out, lse, scale)

@@ -16,7 +16,7 @@ def supported(q: torch.Tensor) -> bool:
     return _lib.available() and q.is_cuda and q.dtype == BF16 and q.dim() == 4 and q.shape[-1] == 128
 
 
-def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None):
+def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None, mask_range=(0, 0)):
     """``outs``: optional ``(dq, dk, dv)`` tensors to write into (contiguous, shaped like ``q``), e.g. regions of a
     symmetric heap that peers will read."""
     B, H, S, D = q.shape
@@ -31,5 +31,6 @@ def backward(dout, q, k, v, out, lse, scale: float, kv_len: int, outs=None):
         if any(t.shape != q.shape for t in (dq, dk, dv)):
             raise _lib.NativeError("gradient outputs must have the shape of q")
     call("tt_attn_bwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(lse), ptr(delta), ptr(dq), ptr(dk), ptr(dv),
-         c_int(B), c_int(H), c_int(S), c_int(kv_len), c_int(pitch), c_float(scale), ptr(status_tensor(q.device)), stream())
+         c_int(B), c_int(H), c_int(S), c_int(kv_len), c_int(mask_range[0]), c_int(mask_range[1]), c_int(pitch), c_float(scale),
+         ptr(status_tensor(q.device)), stream())
     return dq, dk, dv

@@ -25,7 +25,16 @@ def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
             and q.shape == k.shape == v.shape)
 
 
-def forward(q, k, v, kv_valid_len: Optional[int], scale: Optional[float]):
+def _mask(mask_range, kv_len: int):
+    """Normalised ``(lo, hi)`` of the extra masked key range (``(0, 0)``: none)."""
+    if mask_range is None:
+        return 0, 0
+    lo, hi = int(mask_range[0]), min(int(mask_range[1]), kv_len)
+    return (lo, hi) if lo < hi else (0, 0)
+
+
+def forward(q, k, v, kv_valid_len: Optional[int], scale: Optional[float], mask_range=None):
+    """``mask_range = (lo, hi)``: keys in ``[lo, hi)`` are masked in addition to those at and beyond ``kv_valid_len``."""
     B, H, S, D = q.shape
     q, k, v = (check(t.contiguous(), BF16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
     out = torch.empty(B, S, H * D, dtype=BF16, device=q.device)
@@ -33,8 +42,9 @@ def forward(q, k, v, kv_valid_len: Optional[int], scale: Optional[float]):
     lse = torch.full((B, H, pitch), float("inf"), dtype=torch.float32, device=q.device)
     kv_len = S if kv_valid_len is None else min(int(kv_valid_len), S)
     sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    lo, hi = _mask(mask_range, kv_len)
     call("tt_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(B), c_int(H), c_int(S), c_int(kv_len),
-         c_int(pitch), c_float(sc), ptr(status_tensor(q.device)), stream())
+         c_int(lo), c_int(hi), c_int(pitch), c_float(sc), ptr(status_tensor(q.device)), stream())
     return out, lse, q, k, v, sc, kv_len
 
 
@@ -55,7 +65,7 @@ def attention_cache(store: list, mode: str):
         _CACHE, _CACHE_MODE = prev
 
 
-def _forward_cached(q, k, v, kv_valid_len, scale):
+def _forward_cached(q, k, v, kv_valid_len, scale, mask_range=None):
     if _CACHE_MODE == "replay" and _CACHE:
         out, lse = _CACHE.pop(0)
         B, H, S, D = q.shape
@@ -63,7 +73,7 @@ def _forward_cached(q, k, v, kv_valid_len, scale):
         sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
         kv_len = S if kv_valid_len is None else min(int(kv_valid_len), S)
         return out, lse, q, k, v, sc, kv_len
-    res = forward(q, k, v, kv_valid_len, scale)
+    res = forward(q, k, v, kv_valid_len, scale, mask_range)
     if _CACHE_MODE == "record":
         _CACHE.append((res[0], res[1]))
     return res
@@ -71,19 +81,19 @@ def _forward_cached(q, k, v, kv_valid_len, scale):
 
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, kv_valid_len, scale):
-        out, lse, qc, kc, vc, sc, kv_len = _forward_cached(q, k, v, kv_valid_len, scale)
+    def forward(ctx, q, k, v, kv_valid_len, scale, mask_range=None):
+        out, lse, qc, kc, vc, sc, kv_len = _forward_cached(q, k, v, kv_valid_len, scale, mask_range)
         ctx.save_for_backward(qc, kc, vc, out, lse)
-        ctx.sc, ctx.kv_len = sc, kv_len
+        ctx.sc, ctx.kv_len, ctx.mask = sc, kv_len, _mask(mask_range, kv_len)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         from . import attn_backward
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = attn_backward.backward(dout.contiguous(), q, k, v, out, lse, ctx.sc, ctx.kv_len)
-        return dq, dk, dv, None, None
+        dq, dk, dv = attn_backward.backward(dout.contiguous(), q, k, v, out, lse, ctx.sc, ctx.kv_len, mask_range=ctx.mask)
+        return dq, dk, dv, None, None, None
 
 
-def attention(q, k, v, kv_valid_len=None, scale=None):
-    return _Attention.apply(q, k, v, kv_valid_len, scale)
+def attention(q, k, v, kv_valid_len=None, scale=None, mask_range=None):
+    return _Attention.apply(q, k, v, kv_valid_len, scale, mask_range)

@@ -334,9 +334,9 @@ def joint_qkv_projection(x, weight, bias, qw, kw, cos, sin, x2, weight2, bias2, 
 # attention
 # ---------------------------------------------------------------------------------------------
 
-def attention(q, k, v, kv_valid_len=None, scale=None):
+def attention(q, k, v, kv_valid_len=None, scale=None, mask_range=None):
     from . import attention_backend as attn
-    return attn.attention(q, k, v, kv_valid_len, scale)
+    return attn.attention(q, k, v, kv_valid_len, scale, mask_range)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -316,13 +316,14 @@ class _FusedAttentionOutProj(torch.autograd.Function):
     followed by the local output projections of the video and the text stream."""
 
     @staticmethod
-    def forward(ctx, ws, kv_len, scale, private, q, k, v, w, b, wt, bt, extra, extra_t):
+    def forward(ctx, ws, kv_len, mask_range, scale, private, q, k, v, w, b, wt, bt, extra, extra_t):
         from . import attn_tcgen05 as A
         import math
         H_all = ws.heads
         T, s = ws.T, ws.s
         sc = (1.0 / math.sqrt(128)) if scale is None else float(scale)
         kvl = ws.S_tot if kv_len is None else int(kv_len)
+        mlo, mhi = (0, 0) if mask_range is None else (int(mask_range[0]), int(mask_range[1]))
         q, k, v = (check(t.contiguous(), BF16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
         g = ws.heap.tensor(ws.off["g"], (T + s, H_all * 128), BF16)
         ws.heap.barrier()                  # peers are done with the previous gathered buffer / o
@@ -332,7 +333,7 @@ class _FusedAttentionOutProj(torch.autograd.Function):
             pitch = (ws.S_tot + 63) // 64 * 64
             lse = torch.full((1, ws.h_loc, pitch), float("inf"), dtype=torch.float32, device=q.device)
             call("tt_attn_fwd_push", ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(ws.h_loc), c_int(ws.S_tot), c_int(kvl),
-                 c_int(pitch), c_float(sc), ptr(status_tensor(q.device)), stream(), ws.table("g"), c_int(ws.cp),
+                 c_int(mlo), c_int(mhi), c_int(pitch), c_float(sc), ptr(status_tensor(q.device)), stream(), ws.table("g"), c_int(ws.cp),
                  c_int(ws.rank), c_int(T), c_int(s), c_long(H_all * 128))
             if A._CACHE_MODE == "record":
                 A._CACHE.append((out, lse))
@@ -350,7 +351,7 @@ class _FusedAttentionOutProj(torch.autograd.Function):
         ext = None if extra_t is None else check(extra_t.reshape(T, -1).contiguous(), BF16, "extra_t")
         y = _local_gemm_extra(ws, g[T:], ex, w, b)
         yt = _local_gemm_extra(ws, g[:T], ext, wt, bt)
-        ctx.ws, ctx.sc, ctx.kvl = ws, sc, kvl
+        ctx.ws, ctx.sc, ctx.kvl, ctx.mask = ws, sc, kvl, (mlo, mhi)
         if private and any(ctx.needs_input_grad):
             # q / k / v and g live in the workspace every layer shares: keep copies that the next layer cannot overwrite
             COUNTERS["private_saves"] += 1
@@ -400,15 +401,19 @@ class _FusedAttentionOutProj(torch.autograd.Function):
         # dq / dk / dv are written straight into the workspace regions that the peers read in the QKV backward.  Their
         # last readers (the peers' QKV backward of the layer above) finished before the two barriers of this function.
         dq, dk, dv = attn_backward.backward(do_local, q, k, v, out, lse, ctx.sc, ctx.kvl,
-                                            outs=tuple(ws.head_major(n) for n in ("dq", "dk", "dv")))
+                                            outs=tuple(ws.head_major(n) for n in ("dq", "dk", "dv")), mask_range=ctx.mask)
         del dwt_same
-        return (None, None, None, None, dq, dk, dv, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
+        return (None, None, None, None, None, dq, dk, dv, dw, db, dwt, dbt, None if dex is None else dex.view(ctx.extra_shapes[0]), dext)
 
 
-def fused_attention_outproj(ws: UlyssesWorkspace, q, k, v, w, b, wt, bt, extra=None, extra_t=None, kv_len=None, scale=None):
+def fused_attention_outproj(ws: UlyssesWorkspace, q, k, v, w, b, wt, bt, extra=None, extra_t=None, kv_len=None, scale=None,
+                            mask_range=None):
     """``q, k, v [1, heads/cp, T + cp*s, 128]`` -> (projection of this rank's video tokens with ``w``, projection of the
-    text tokens with ``wt``); ``extra`` / ``extra_t`` are local tensors concatenated to the attention output along K."""
-    return _FusedAttentionOutProj.apply(ws, kv_len, scale, saves_need_private_copies(), q, k, v, w, b, wt, bt, extra, extra_t)
+    text tokens with ``wt``); ``extra`` / ``extra_t`` are local tensors concatenated to the attention output along K.
+    Keys at and beyond ``kv_len`` (context-parallel padding, the sequence tail) and keys in ``mask_range`` (padded text
+    tokens, which come first in this layout) are masked."""
+    return _FusedAttentionOutProj.apply(ws, kv_len, mask_range, scale, saves_need_private_copies(), q, k, v, w, b, wt, bt,
+                                        extra, extra_t)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -606,3 +611,20 @@ def fused_param_all_gather(heap: SymmetricHeap, param_off: int, start: int, src:
     """Write this rank's updated parameter shard into every rank's parameter buffer at ``start``."""
     call("tt_all_gather_push_bf16", heap.ptr_table(param_off), c_int(heap.world), c_long(start), ptr(src),
          c_long(src.numel()), stream())
+
+
+def fused_reduce_adamw_all_gather(heap: SymmetricHeap, grad_off: int, param_off: int, start: int, count: int,
+                                  exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, master: Optional[torch.Tensor],
+                                  master_lo: Optional[torch.Tensor], *, lr: float, beta1: float, beta2: float, eps: float,
+                                  weight_decay: float, step: int, grad_scale: float, grads_reduced: bool = False) -> None:
+    """One kernel for ``[start, start + count)`` of the flat buffers that live in ``heap``: sum every rank's bf16
+    gradients (peer loads) times ``grad_scale``, AdamW on this rank's moments / master weights, and store the new bf16
+    weights into every rank's parameter buffer (peer stores).  ``grads_reduced``: the local gradient buffer already
+    holds the reduced shard (overlapped reduce-scatter), so only it is read.  The caller brackets the optimizer step
+    with ``heap.barrier()``: gradients complete everywhere before, all loads and stores done after."""
+    state_bf16 = exp_avg.dtype == BF16
+    gt = _table([heap.local_ptr + grad_off]) if grads_reduced else heap.ptr_table(grad_off)
+    call("tt_rs_adamw_ag", gt, c_int(1 if grads_reduced else heap.world), heap.ptr_table(param_off), c_int(heap.world),
+         c_int(heap.rank), c_long(start), ptr(exp_avg), ptr(exp_avg_sq), ptr(master), ptr(master_lo), c_long(count),
+         c_int(1 if state_bf16 else 0), c_float(lr), c_float(beta1), c_float(beta2), c_float(eps), c_float(weight_decay),
+         c_int(step), c_float(grad_scale), stream())

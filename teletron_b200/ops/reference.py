@@ -87,19 +87,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-              kv_valid_len: Optional[int] = None, scale: Optional[float] = None) -> torch.Tensor:
+              kv_valid_len: Optional[int] = None, scale: Optional[float] = None, mask_range=None) -> torch.Tensor:
     """Non-causal softmax attention.
 
     ``q, k, v`` are ``[B, h, S, D]``; the result is ``[B, S, h * D]`` (token-major,
     the layout the output projection consumes).  ``kv_valid_len`` masks keys at
-    positions ``>= kv_valid_len`` (padded text tokens sit at the sequence tail); the
-    reference never applies its mask (``dit_attention.py:313``), so ``None`` is the
-    parity setting.
+    positions ``>= kv_valid_len`` (padded text tokens sit at the sequence tail) and
+    ``mask_range = (lo, hi)`` masks keys in ``[lo, hi)`` (padded text tokens when the text
+    comes first); the reference never applies its mask (``dit_attention.py:313``), so
+    ``None`` is the parity setting.
     """
     B, h, S, D = q.shape
-    if kv_valid_len is not None and kv_valid_len < k.shape[2]:
-        mask = torch.zeros(1, 1, 1, k.shape[2], dtype=torch.bool, device=q.device)
-        mask[..., :kv_valid_len] = True
+    n = k.shape[2]
+    tail = kv_valid_len is not None and kv_valid_len < n
+    mid = mask_range is not None and mask_range[0] < mask_range[1]
+    if tail or mid:
+        mask = torch.ones(1, 1, 1, n, dtype=torch.bool, device=q.device)
+        if tail:
+            mask[..., kv_valid_len:] = False
+        if mid:
+            mask[..., mask_range[0]:mask_range[1]] = False
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, scale=scale)
     else:
         o = F.scaled_dot_product_attention(q, k, v, scale=scale)

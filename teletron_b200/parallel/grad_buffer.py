@@ -187,6 +187,9 @@ class DistributedDataParallel(nn.Module):
                 return self.heap.tensor(po, (numel,), dtype), self.heap.tensor(go, (numel,), grad_dtype)
         self.buffers = [ParamAndGradBuffer(v, self.world, bucket_bytes, grad_dtype, storage) for v in by_dtype.values()]
         self.grad_scale = 1.0 / self.world
+        # Set by the optimizer when it reduces the gradients itself, inside its fused reduce-scatter + AdamW + all-gather
+        # kernel: finish_grad_sync then only makes every rank's gradients complete and visible.
+        self.reduce_in_optimizer = False
         self._sync_enabled = True
         self._hooks = []
         self.tp_group = tp_group
@@ -291,6 +294,13 @@ class DistributedDataParallel(nn.Module):
             return
         if self.heap is not None:
             self.heap.barrier()        # every rank's gradients are complete before anyone reads them
+        if self.reduce_in_optimizer and self.heap is not None:
+            if self.check_for_nan_in_grad:
+                for buf in self.buffers:
+                    if not torch.isfinite(buf.grad_data.float().sum()):
+                        raise RuntimeError("non-finite gradient")
+            self._reset_pending()
+            return
         for buf in self.buffers:
             for b in buf.buckets:
                 if b.handle is None:

@@ -78,6 +78,14 @@ class DistributedOptimizer:
                 states.append(_ShardState(buf, s, e, mm, state_dtype))
             self.shards.append(states)
         self.last_grad_norm: Optional[float] = None
+        # With the flat buffers in a symmetric heap, the whole update of a shard is one kernel: peers' gradients are
+        # read and summed, AdamW runs, and the new weights are stored into every replica (csrc/optim.cu).  Without
+        # clipping nothing needs the reduced gradients beforehand, so the separate reduce-scatter is dropped as well;
+        # with overlapped reduction (side stream during backward) the kernel reads the already reduced local shard.
+        self.fused_update = (self.sharded and getattr(ddp, "heap", None) is not None and len(ddp.buffers) == 1
+                             and ddp.buffers[0].dtype == torch.bfloat16)
+        self.reduce_here = self.fused_update and not (clip_grad and clip_grad > 0.0) and not ddp.overlap_grad_reduce
+        ddp.reduce_in_optimizer = self.reduce_here
 
     # ---- helpers ------------------------------------------------------------------------
     def _segments(self, buf: ParamAndGradBuffer, st: _ShardState):
@@ -121,6 +129,23 @@ class DistributedOptimizer:
                 return False
             clip_coef = min(1.0, self.clip_grad / (norm + 1e-6))
         b1, b2 = self.betas
+        if self.fused_update:
+            from ..ops import fused_comm as FC
+            heap, (po, go) = self.ddp.heap, self.ddp.heap_offsets
+            buf, states = self.ddp.buffers[0], self.shards[0]
+            scale = clip_coef * (self.ddp.grad_scale if self.reduce_here else 1.0)
+            for st in states:
+                for s, e, r in self._segments(buf, st):
+                    o0, o1 = s - st.start, e - st.start
+                    FC.fused_reduce_adamw_all_gather(
+                        heap, go, po, s, e - s, st.exp_avg[o0:o1], st.exp_avg_sq[o0:o1],
+                        None if st.master is None else st.master[o0:o1],
+                        None if st.master_lo is None else st.master_lo[o0:o1],
+                        lr=self.lr, beta1=b1, beta2=b2, eps=self.eps,
+                        weight_decay=self.weight_decay if r.weight_decay else 0.0, step=self.step_count,
+                        grad_scale=scale, grads_reduced=not self.reduce_here)
+            heap.barrier()         # peers have read this rank's gradients; every replica holds the new weights
+            return True
         for buf, states in zip(self.ddp.buffers, self.shards):
             for st in states:
                 for s, e, r in self._segments(buf, st):

@@ -54,11 +54,38 @@ def test_round_trip_through_tp2_files_and_model_load(tmp_path):
     torch.testing.assert_close(po, torch.cat([full_po[:, :H // 2], full_po[:, H:H + F // 2]], dim=1))
     # back to HF names: identical to the source
     back = tmp_path / "hf_back"
-    C.convert_tel_to_hf(str(out), str(back), torch.float32, cfg.num_attention_heads, cfg.hidden_size, cfg.mlp_hidden)
-    hf2 = torch.load(back / "diffusion_pytorch_model.pt")
+    C.convert_tel_to_hf(str(out), str(back), torch.float32, cfg.num_attention_heads, cfg.hidden_size, cfg.mlp_hidden,
+                        max_shard_size="300KB")
+    # a diffusers-style folder: numbered safetensors shards, the index that maps every tensor to its shard, config.json
+    import json
+    from safetensors.torch import load_file
+    index = json.load(open(back / "diffusion_pytorch_model.safetensors.index.json"))
+    shard_names = sorted(set(index["weight_map"].values()))
+    assert len(shard_names) > 1 and all(n.startswith("diffusion_pytorch_model-000") and n.endswith(f"-of-{len(shard_names):05d}.safetensors")
+                                        for n in shard_names)
+    assert set(index["weight_map"]) == set(hf)
+    assert index["metadata"]["total_size"] == sum(v.numel() * v.element_size() for v in hf.values())
+    hf2 = {}
+    for n in shard_names:
+        part = load_file(str(back / n))
+        assert all(index["weight_map"][k] == n for k in part)
+        hf2.update(part)
     assert set(hf2) == set(hf)
     for k in hf:
         torch.testing.assert_close(hf2[k], hf[k], rtol=0, atol=0)
+    conf = json.load(open(back / "config.json"))
+    assert conf["num_layers"] == cfg.num_layers and conf["num_single_layers"] == cfg.num_single_layers
+    assert conf["num_attention_heads"] == cfg.num_attention_heads and conf["_class_name"] == "HunyuanVideoTransformer3DModel"
+    # the converter reads its own output back (HF folder -> TeleTron), and one shard when everything fits
+    again = tmp_path / "tel_again"
+    C.convert_hf_to_tel(str(back), str(again), tp=1, dtype=torch.float32, heads=cfg.num_attention_heads,
+                        hidden=cfg.hidden_size, mlp_hidden=cfg.mlp_hidden)
+    single = tmp_path / "hf_single"
+    C.convert_tel_to_hf(str(again), str(single), torch.float32, cfg.num_attention_heads, cfg.hidden_size, cfg.mlp_hidden)
+    assert (single / "diffusion_pytorch_model.safetensors").is_file() and not (single / "diffusion_pytorch_model.safetensors.index.json").exists()
+    one_file = load_file(str(single / "diffusion_pytorch_model.safetensors"))
+    for k in hf:
+        torch.testing.assert_close(one_file[k], hf[k], rtol=0, atol=0)
     # a TP=1 conversion loads into the model by name (training's loader strips the prefix)
     one = tmp_path / "tel1"
     C.convert_hf_to_tel(str(src), str(one), tp=1, dtype=torch.float32, heads=cfg.num_attention_heads,

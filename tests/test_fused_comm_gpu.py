@@ -227,7 +227,11 @@ def test_fused_ulysses_several_layers_without_per_block_recompute():
         gen = torch.Generator().manual_seed(0)
         batch = {"latents": torch.randn(1, 16, 3, 30, 34, generator=gen), "prompt_embeds": torch.randn(1, 40, 4096, generator=gen),
                  "clip_text_embed": torch.randn(1, 768, generator=gen)}
-        for kw in (dict(recompute_granularity=None), dict(recompute_granularity="full", recompute_method="uniform", recompute_num_layers=2)):
+        mask = torch.zeros(1, 40, dtype=torch.bool)
+        mask[:, :25] = True                     # 15 padded text tokens: a masked key range at the head of the fused layout
+        batch["prompt_attention_mask"] = mask
+        for kw in (dict(recompute_granularity=None, apply_text_mask=True),
+                   dict(recompute_granularity="full", recompute_method="uniform", recompute_num_layers=2)):
             cfg = hunyuan_13b(in_channels=16, num_layers=2, num_single_layers=2, **kw)
             res = {}
             for fused in (True, False):
