@@ -39,7 +39,8 @@ def main():
     p.add_argument("--ref_frame", type=str, default="")
     p.add_argument("--prompt", type=str, required=True)
     p.add_argument("--device", type=str, default="cuda:0")
-    p.add_argument("--output_file", type=str, default="output.pt")
+    p.add_argument("--output_file", type=str, default="output.mp4")
+    p.add_argument("--fps", type=float, default=15.0)
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--guidance_scale", type=float, default=4.0)
     p.add_argument("--embedded_guidance_scale", type=float, default=1.0)
@@ -55,8 +56,8 @@ def main():
                num_inference_steps=a.num_inference_steps, seed=a.seed, model_type=a.model_type, ref_images=ref,
                guidance_scale=a.guidance_scale, embedded_guidance_scale=a.embedded_guidance_scale,
                cfg_zero_star=a.cfg_zero_star)
-    save_video_tensor(out.frames[0], a.output_file)
-    print(f"wrote {tuple(out.frames[0].shape)} frames to {a.output_file}")
+    written = save_video_tensor(out.frames[0], a.output_file, fps=a.fps)
+    print(f"wrote {tuple(out.frames[0].shape)} frames to {written}")
 
 
 if __name__ == "__main__":

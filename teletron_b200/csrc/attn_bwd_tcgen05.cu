@@ -309,6 +309,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float4* lse4 = reinterpret_cast<const float4*>(p.lse + (long)bh * p.pitch + col0);
             const float4* del4 = reinterpret_cast<const float4*>(p.delta + (long)bh * p.pitch + col0);
             uint32_t pk[16];
+            // query-stationary: only a chunk that straddles the key length or the masked key range needs per-key tests
+#ifdef TT_ATTN_NO_RANGE_MASK
+            const bool chunk_clean = false;
+#else
+            const bool chunk_clean = KVS || ((c + 1) * BC <= p.kv_len &&
+                                             (p.mask_lo >= p.mask_hi || p.mask_hi <= c * BC || p.mask_lo >= (c + 1) * BC));
+#endif
             if (!mbar_wait(s_full, par, &abort_flag)) goto done;
             tc_fence_after();
             {
@@ -336,10 +343,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     float2 pr = make_float2(exp2f(x.x), exp2f(x.y));
                     if (KVS) {
                         if (!row_live) pr = make_float2(0.f, 0.f);
-                    } else {
+                    } else if (!chunk_clean) {
                         const int cc = col0 + pass * 32 + 2 * i;
+#ifdef TT_ATTN_NO_RANGE_MASK
+                        if (cc >= p.kv_len) pr.x = 0.f;
+                        if (cc + 1 >= p.kv_len) pr.y = 0.f;
+#else
                         if (cc >= p.kv_len || (cc >= p.mask_lo && cc < p.mask_hi)) pr.x = 0.f;
                         if (cc + 1 >= p.kv_len || (cc + 1 >= p.mask_lo && cc + 1 < p.mask_hi)) pr.y = 0.f;
+#endif
                     }
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(pr.x, pr.y);
                     pk[pass * 16 + i] = *reinterpret_cast<const uint32_t*>(&pb);

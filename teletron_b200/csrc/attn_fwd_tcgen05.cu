@@ -202,8 +202,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             if (!mbar_wait(s_full(t), (uint32_t)j & 1u, &abort_flag)) goto done;
             tc_fence_after();
             const int valid = p.kv_len - j * BKV;      // columns >= valid are masked (only in the last tile)
+#ifdef TT_ATTN_NO_RANGE_MASK
+            const int lo = 0, hi = 0;
+            const bool full_tile = valid >= BKV;
+#else
             const int lo = p.mask_lo - j * BKV, hi = p.mask_hi - j * BKV;      // and columns [lo, hi) of this tile
             const bool full_tile = valid >= BKV && (lo >= hi || hi <= 0 || lo >= BKV);
+#endif
             // pass 1: row maximum (3-input max, four independent chains)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll

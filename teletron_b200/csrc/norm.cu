@@ -20,12 +20,16 @@ constexpr int kMaxCols = 8192;
 // forward: one warp per row, the row lives in registers
 // ---------------------------------------------------------------------------------------------
 template <int VPL, bool GATE>
-__global__ void __launch_bounds__(256) ln_mod_fwd_kernel(
+__global__ void __launch_bounds__(256, (VPL <= 12 ? 3 : 1)) ln_mod_fwd_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ branch,
     const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ scale,
     const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ new_res,
     __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
     long rows, int cols, long rows_per_batch, float eps) {
+    // The row stays in registers as packed bf16 (4 registers per 8 elements) and is unpacked in each of the three
+    // passes: that keeps the kernel under 85 registers, so three CTAs (24 warps, each with a whole row of loads in
+    // flight) share an SM.  With the fp32 copy it needed 150 registers and ran one CTA per SM at 0.47 of the copy
+    // bandwidth.
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int nvec = cols >> 3;
@@ -34,26 +38,32 @@ __global__ void __launch_bounds__(256) ln_mod_fwd_kernel(
          row += (long)gridDim.x * warps_per_cta) {
         const long b = row / rows_per_batch;
         const __nv_bfloat16* xr = x + row * cols;
-        float v[VPL][8];
+        bf16x8 pk[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = lane + i * 32;
+            if (c < nvec) pk[i] = ld8(xr + c * 8);
+        }
         float sum = 0.f;
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             const int c = lane + i * 32;
             if (c < nvec) {
-                unpack8(ld8(xr + c * 8), v[i]);
+                float v[8];
+                unpack8(pk[i], v);
                 if (GATE) {
                     float br[8], g[8];
                     unpack8(ld8(branch + row * cols + c * 8), br);
                     unpack8(ld8(gate + b * cols + c * 8), g);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] + g[j] * br[j];
+                    for (int j = 0; j < 8; ++j) v[j] = v[j] + g[j] * br[j];
                     // the residual stream is stored in bf16: normalise exactly what is stored
-                    bf16x8 packed = pack8(v[i]);
-                    st8(new_res + row * cols + c * 8, packed);
-                    unpack8(packed, v[i]);
+                    pk[i] = pack8(v);
+                    st8(new_res + row * cols + c * 8, pk[i]);
+                    unpack8(pk[i], v);
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) sum += v[i][j];
+                for (int j = 0; j < 8; ++j) sum += v[j];
             }
         }
         const float mean = warp_sum(sum) * inv_cols;
@@ -61,9 +71,11 @@ __global__ void __launch_bounds__(256) ln_mod_fwd_kernel(
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             if (lane + i * 32 < nvec) {
+                float v[8];
+                unpack8(pk[i], v);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const float d = v[i][j] - mean;
+                    const float d = v[j] - mean;
                     sq += d * d;
                 }
             }
@@ -77,11 +89,12 @@ __global__ void __launch_bounds__(256) ln_mod_fwd_kernel(
         for (int i = 0; i < VPL; ++i) {
             const int c = lane + i * 32;
             if (c < nvec) {
-                float sc[8], sh[8], o[8];
+                float v[8], sc[8], sh[8], o[8];
+                unpack8(pk[i], v);
                 unpack8(ld8(scale + b * cols + c * 8), sc);
                 unpack8(ld8(shift + b * cols + c * 8), sh);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * (1.f + sc[j]) + sh[j];
+                for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * (1.f + sc[j]) + sh[j];
                 st8(y + row * cols + c * 8, pack8(o));
             }
         }
@@ -92,6 +105,41 @@ __global__ void __launch_bounds__(256) ln_mod_fwd_kernel(
 // backward: one CTA walks rows, thread t owns columns [8t, 8t+8); column sums stay in registers
 // ---------------------------------------------------------------------------------------------
 // partials layout: [batch][blocks_per_batch][K][cols] fp32 with K = 2 (dscale, dshift) or 3 (+dgate)
+//
+// kRowBatch rows go through one block-wide reduction together: a thread first issues the loads of all of them (8 x 16 bytes in
+// flight instead of 2) and the CTA pays one barrier pair per batch instead of per row.
+constexpr int kRowBatch = 4;
+
+// Sums of 8 values (2 per row of the batch) over the CTA; every thread gets all of them.  Shuffles are the scarce resource
+// here (one warp-wide shuffle per clock and SM), so the eight warp sums are formed together: in each of the first three
+// butterfly steps a lane hands half of its values to its partner and keeps the other half (4 + 2 + 1 shuffles), two more
+// steps finish the one value left (lane 4q ends up with value q): 9 shuffles instead of 40.  `red` holds [2][8][32]
+// floats and is used alternately (parity), so one barrier per call is enough.
+static_assert(kRowBatch == 4, "block_sum_batch reduces exactly eight values");
+__device__ __forceinline__ void block_sum_batch(float* v, float* red, int parity) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float* r = red + parity * (8 * 32);
+    float a[4], b2[2];
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = (h16 ? v[i + 4] : v[i]) + __shfl_xor_sync(0xffffffffu, h16 ? v[i] : v[i + 4], 16);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) b2[i] = (h8 ? a[i + 2] : a[i]) + __shfl_xor_sync(0xffffffffu, h8 ? a[i] : a[i + 2], 8);
+    float c = (h4 ? b2[1] : b2[0]) + __shfl_xor_sync(0xffffffffu, h4 ? b2[0] : b2[1], 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    if ((lane & 3) == 0) r[(lane >> 2) * 32 + warp] = c;        // value q = 4 * bit4 + 2 * bit3 + bit2 = lane >> 2
+    __syncthreads();
+    // lane L sums the warps w = L / 8, L / 8 + 4, ... of value L % 8, the four parts meet by two shuffles
+    float t = 0.f;
+    for (int w = lane >> 3; w < nwarps; w += 4) t += r[(lane & 7) * 32 + w];
+    t += __shfl_xor_sync(0xffffffffu, t, 8);
+    t += __shfl_xor_sync(0xffffffffu, t, 16);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = __shfl_sync(0xffffffffu, t, q);
+}
+
 template <bool GATE, int MAXT>
 __global__ void __launch_bounds__(MAXT) ln_mod_bwd_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ dres_in,
@@ -99,7 +147,7 @@ __global__ void __launch_bounds__(MAXT) ln_mod_bwd_kernel(
     const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ scale,
     const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
     __nv_bfloat16* __restrict__ dbranch, float* __restrict__ partials, int cols, long rows_per_batch) {
-    __shared__ float red[64];
+    __shared__ float red[2 * 8 * 32];
     const int nvec = cols >> 3;
     const int t = threadIdx.x;
     const bool active = t < nvec;
@@ -119,47 +167,77 @@ __global__ void __launch_bounds__(MAXT) ln_mod_bwd_kernel(
         for (int j = 0; j < 8; ++j) sc1[j] += 1.f;
         if (GATE) unpack8(ld8(gate + b * cols + t * 8), gt);
     }
-    for (long r = blockIdx.x; r < rows_per_batch; r += gridDim.x) {
-        const long row = b * rows_per_batch + r;
-        float g[8], xh[8], dyv[8];
-        float s1 = 0.f, s2 = 0.f;
-        const float mu = mean[row], rs = rstd[row];
-        if (active) {
-            float xv[8];
-            unpack8(ld8(dy + row * cols + t * 8), dyv);
-            unpack8(ld8(x + row * cols + t * 8), xv);
+    int parity = 0;
+    for (long r0 = (long)blockIdx.x * kRowBatch; r0 < rows_per_batch; r0 += (long)gridDim.x * kRowBatch, parity ^= 1) {
+        bf16x8 pdy[kRowBatch], px[kRowBatch];
+        float mu[kRowBatch], rs[kRowBatch], sums[2 * kRowBatch];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                xh[j] = (xv[j] - mu) * rs;
-                g[j] = dyv[j] * sc1[j];
-                s1 += g[j];
-                s2 += g[j] * xh[j];
-                acc_scale[j] += dyv[j] * xh[j];
-                acc_shift[j] += dyv[j];
+        for (int k = 0; k < kRowBatch; ++k) {
+            const bool live = r0 + k < rows_per_batch;
+            const long row = b * rows_per_batch + (live ? r0 + k : r0);
+            mu[k] = mean[row];
+            rs[k] = rstd[row];
+            if (active && live) {
+                pdy[k] = ld8(dy + row * cols + t * 8);
+                px[k] = ld8(x + row * cols + t * 8);
+            } else {
+                const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                pdy[k] = pack8(z);
+                px[k] = pack8(z);
+                if (!live) mu[k] = 0.f;      // padded row: x - mu = 0, dy = 0, nothing accumulates
             }
         }
-        const float2 s = block_sum2(s1, s2, red);
-        if (active) {
-            const float m1 = s.x * inv_cols, m2 = s.y * inv_cols;
-            float d[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) d[j] = rs * (g[j] - m1 - xh[j] * m2);
-            if (dres_in != nullptr) {
-                float up[8];
-                unpack8(ld8(dres_in + row * cols + t * 8), up);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) d[j] += up[j];
-            }
-            st8(dx + row * cols + t * 8, pack8(d));
-            if (GATE) {
-                float br[8], db[8];
-                unpack8(ld8(branch + row * cols + t * 8), br);
+        for (int k = 0; k < kRowBatch; ++k) {
+            float dyv[8], xv[8];
+            unpack8(pdy[k], dyv);
+            unpack8(px[k], xv);
+            float s1 = 0.f, s2 = 0.f;
+            if (active) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    acc_gate[j] += d[j] * br[j];
-                    db[j] = d[j] * gt[j];
+                    const float xh = (xv[j] - mu[k]) * rs[k];
+                    const float g = dyv[j] * sc1[j];
+                    s1 += g;
+                    s2 += g * xh;
+                    acc_scale[j] += dyv[j] * xh;
+                    acc_shift[j] += dyv[j];
                 }
-                st8(dbranch + row * cols + t * 8, pack8(db));
+            }
+            sums[2 * k] = s1;
+            sums[2 * k + 1] = s2;
+        }
+        block_sum_batch(sums, red, parity);
+#pragma unroll
+        for (int k = 0; k < kRowBatch; ++k) {
+            if (active && r0 + k < rows_per_batch) {
+                const long row = b * rows_per_batch + r0 + k;
+                const float m1 = sums[2 * k] * inv_cols, m2 = sums[2 * k + 1] * inv_cols;
+                float dyv[8], xv[8], d[8];
+                unpack8(pdy[k], dyv);
+                unpack8(px[k], xv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float xh = (xv[j] - mu[k]) * rs[k];
+                    d[j] = rs[k] * (dyv[j] * sc1[j] - m1 - xh * m2);
+                }
+                if (dres_in != nullptr) {
+                    float up[8];
+                    unpack8(ld8(dres_in + row * cols + t * 8), up);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) d[j] += up[j];
+                }
+                st8(dx + row * cols + t * 8, pack8(d));
+                if (GATE) {
+                    float br[8], db[8];
+                    unpack8(ld8(branch + row * cols + t * 8), br);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        acc_gate[j] += d[j] * br[j];
+                        db[j] = d[j] * gt[j];
+                    }
+                    st8(dbranch + row * cols + t * 8, pack8(db));
+                }
             }
         }
     }
@@ -239,17 +317,32 @@ __global__ void __launch_bounds__(1024) gate_residual_bwd_kernel(const __nv_bflo
     unpack8(ld8(gate + b * cols + t * 8), gt);
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (long r = blockIdx.x; r < rows_per_batch; r += gridDim.x) {
-        const long row = b * rows_per_batch + r;
-        float d[8], br[8], db[8];
-        unpack8(ld8(dout + row * cols + t * 8), d);
-        unpack8(ld8(branch + row * cols + t * 8), br);
+    // four rows per iteration: eight 16-byte loads in flight per thread
+    for (long r0 = (long)blockIdx.x * 4; r0 < rows_per_batch; r0 += (long)gridDim.x * 4) {
+        bf16x8 pd[4], pb[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            acc[j] += d[j] * br[j];
-            db[j] = d[j] * gt[j];
+        for (int k = 0; k < 4; ++k) {
+            if (r0 + k < rows_per_batch) {
+                const long row = b * rows_per_batch + r0 + k;
+                pd[k] = ld8(dout + row * cols + t * 8);
+                pb[k] = ld8(branch + row * cols + t * 8);
+            }
         }
-        st8(dbranch + row * cols + t * 8, pack8(db));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (r0 + k < rows_per_batch) {
+                const long row = b * rows_per_batch + r0 + k;
+                float d[8], br[8], db[8];
+                unpack8(pd[k], d);
+                unpack8(pb[k], br);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[j] += d[j] * br[j];
+                    db[j] = d[j] * gt[j];
+                }
+                st8(dbranch + row * cols + t * 8, pack8(db));
+            }
+        }
     }
     float* p = partials + (b * gridDim.x + blockIdx.x) * (long)cols + t * 8;
 #pragma unroll
@@ -342,6 +435,138 @@ __global__ void __launch_bounds__(1024) rmsnorm_bwd_kernel(const __nv_bfloat16* 
         float* p = partials + (long)blockIdx.x * cols + t * 8;
 #pragma unroll
         for (int j = 0; j < 8; ++j) p[j] = acc[j];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm for short rows (cols <= 256, e.g. the per-head norm with cols = 128): LPR lanes per row, 32 / LPR rows per
+// warp and two such groups per iteration, so that every lane has work and several 16-byte loads in flight.  With one
+// warp per row half of the lanes idled (forward) and the backward ran 32-thread CTAs.
+// ---------------------------------------------------------------------------------------------
+template <int LPR>
+__device__ __forceinline__ float row_sum(float v) {
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_small_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
+                                                               long rows, int cols, float eps) {
+    constexpr int RPW = 32 / LPR, U = 4;
+    const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
+    const int nvec = cols >> 3;
+    const bool col_ok = l < nvec;
+    const long warp_id = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long nwarps = (long)gridDim.x * (blockDim.x >> 5);
+    float wv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] = 0.f;
+    if (col_ok) unpack8(ld8(w + l * 8), wv);
+    const float inv_cols = 1.f / (float)cols;
+    for (long base = warp_id * (RPW * U); base < rows; base += nwarps * (RPW * U)) {
+        bf16x8 pk[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long row = base + u * RPW + sub;
+            if (row < rows && col_ok) pk[u] = ld8(x + row * cols + l * 8);
+            else pk[u] = bf16x8{};
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long row = base + u * RPW + sub;
+            float v[8], o[8];
+            unpack8(pk[u], v);
+            float sq = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
+            const float rstd = rsqrtf(row_sum<LPR>(sq) * inv_cols + eps);
+            if (row < rows) {
+                if (l == 0) rstd_out[row] = rstd;
+                if (col_ok) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = v[j] * rstd * wv[j];
+                    st8(y + row * cols + l * 8, pack8(o));
+                }
+            }
+        }
+    }
+}
+
+// partials [gridDim.x][cols]: per-CTA column sums of dy * xhat (summed by column_finalize_kernel)
+template <int LPR>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                               const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               const float* __restrict__ rstd,
+                                                               __nv_bfloat16* __restrict__ dx, float* __restrict__ partials,
+                                                               long rows, int cols) {
+    constexpr int RPW = 32 / LPR, U = 4;
+    __shared__ float fold[8][LPR * 8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane / LPR, l = lane % LPR;
+    const int nvec = cols >> 3;
+    const bool col_ok = l < nvec;
+    const long warp_id = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+    const long nwarps = (long)gridDim.x * (blockDim.x >> 5);
+    float wv[8], acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        wv[j] = 0.f;
+        acc[j] = 0.f;
+    }
+    if (col_ok) unpack8(ld8(w + l * 8), wv);
+    const float inv_cols = 1.f / (float)cols;
+    for (long base = warp_id * (RPW * U); base < rows; base += nwarps * (RPW * U)) {
+        bf16x8 pd[U], px[U];
+        float rs[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long row = base + u * RPW + sub;
+            const bool ok = row < rows && col_ok;
+            pd[u] = ok ? ld8(dy + row * cols + l * 8) : bf16x8{};
+            px[u] = ok ? ld8(x + row * cols + l * 8) : bf16x8{};
+            rs[u] = row < rows ? rstd[row] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long row = base + u * RPW + sub;
+            float d[8], xv[8], g[8], xh[8], o[8];
+            unpack8(pd[u], d);
+            unpack8(px[u], xv);
+            float sdot = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                xh[j] = xv[j] * rs[u];
+                g[j] = d[j] * wv[j];
+                sdot += g[j] * xh[j];
+                acc[j] += d[j] * xh[j];
+            }
+            const float m = row_sum<LPR>(sdot) * inv_cols;
+            if (row < rows && col_ok) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = rs[u] * (g[j] - xh[j] * m);
+                st8(dx + row * cols + l * 8, pack8(o));
+            }
+        }
+    }
+    // fold the RPW row groups of the warp (lanes l, l + LPR, ... own the same columns), then the warps of the CTA
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int o = LPR; o < 32; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    }
+    if (sub == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) fold[warp][l * 8 + j] = acc[j];
+    }
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float sacc = 0.f;
+        for (int q = 0; q < nw; ++q) sacc += fold[q][c];
+        partials[(long)blockIdx.x * cols + c] = sacc;
     }
 }
 
@@ -469,6 +694,20 @@ extern "C" int tt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
     long want = (rows + 7) / 8;
     const int grid = (int)(want < 148L * 16 ? want : 148L * 16);
     const int vpl = ((cols >> 3) + 31) / 32;
+    if (cols <= 256) {
+        // short rows: several rows per warp
+        const int nvec = cols >> 3;
+        long need = (rows + 63) / 64;
+        const int g2 = (int)(need < 148L * 8 ? need : 148L * 8);
+#define RMS_SMALL(LPR) rmsnorm_fwd_small_kernel<LPR><<<g2, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, cols, eps)
+        if (nvec <= 4) RMS_SMALL(4);
+        else if (nvec <= 8) RMS_SMALL(8);
+        else if (nvec <= 16) RMS_SMALL(16);
+        else RMS_SMALL(32);
+#undef RMS_SMALL
+        TT_CHECK_LAUNCH();
+        return TT_OK;
+    }
     if (vpl <= 1) LAUNCH_RMS(1);
     else if (vpl <= 4) LAUNCH_RMS(4);
     else if (vpl <= 12) LAUNCH_RMS(12);
@@ -478,14 +717,32 @@ extern "C" int tt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
     return TT_OK;
 }
 
+namespace {
+// first pass of the RMSNorm backward into `nblk` partial rows: rows-per-warp kernel for short rows, CTA-per-row otherwise
+void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* partials,
+                        long rows, int cols, int nblk, cudaStream_t st) {
+    if (cols <= 256) {
+        const int nvec = cols >> 3;
+#define RMS_BWD_SMALL(LPR) rmsnorm_bwd_small_kernel<LPR><<<nblk, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols)
+        if (nvec <= 4) RMS_BWD_SMALL(4);
+        else if (nvec <= 8) RMS_BWD_SMALL(8);
+        else if (nvec <= 16) RMS_BWD_SMALL(16);
+        else RMS_BWD_SMALL(32);
+#undef RMS_BWD_SMALL
+        return;
+    }
+    const int threads = (((cols >> 3) + 31) / 32) * 32;
+    rmsnorm_bwd_kernel<<<nblk, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                 (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols);
+}
+}  // namespace
+
 extern "C" int tt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                               float* partials, void* dw, long rows, int cols, void* stream) {
     if (bad_cols(cols) || rows <= 0) return TT_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const int nblk = pick_blocks(rows, 1);
-    const int threads = (((cols >> 3) + 31) / 32) * 32;
-    rmsnorm_bwd_kernel<<<nblk, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                 (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols);
+    launch_rmsnorm_bwd(dy, x, w, rstd, dx, partials, rows, cols, nblk, st);
     TT_CHECK_LAUNCH();
     column_finalize_kernel<<<dim3((cols + 255) / 256, 1, 1), 256, 0, st>>>(partials, (__nv_bfloat16*)dw, nullptr, nullptr,
                                                                          1, nblk, cols);
@@ -531,11 +788,9 @@ extern "C" int tt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
     int nblk = pick_blocks(rows, 1);
     if (nblk > TT_NOALLOC_MAX_BLOCKS) nblk = TT_NOALLOC_MAX_BLOCKS;
     cudaStream_t st = (cudaStream_t)stream;
-    const int threads = (((cols >> 3) + 31) / 32) * 32;
     // every one of the nblk partial rows is fully rewritten by its block before the finalize pass reads it,
     // so nothing left behind by an earlier call can leak into this one
-    rmsnorm_bwd_kernel<<<nblk, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                 (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, partials, rows, cols);
+    launch_rmsnorm_bwd(dy, x, w, rstd, dx, partials, rows, cols, nblk, st);
     TT_CHECK_LAUNCH();
     column_finalize_kernel<<<dim3((cols + 255) / 256, 1, 1), 256, 0, st>>>(partials, (__nv_bfloat16*)dw, nullptr, nullptr,
                                                                          1, nblk, cols);

@@ -34,56 +34,102 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, const float* f) {
     *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(&r);
 }
 
-__global__ void __launch_bounds__(256) qkv_post_fwd_kernel(
+// Sum over the 16 lanes that share one (token, head) item.
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// RoPE on 8 consecutive elements (4 interleaved pairs) with per-element tables; `t` = +1 forward, -1 transpose.
+__device__ __forceinline__ void rope8(float* v, const float* c, const float* s) {
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        const float a0 = v[i], a1 = v[i + 1];
+        v[i] = a0 * c[i] - a1 * s[i];
+        v[i + 1] = a1 * c[i + 1] + a0 * s[i + 1];
+    }
+}
+__device__ __forceinline__ void rope8_transpose(float* v, const float* c, const float* s) {
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        const float a0 = v[i], a1 = v[i + 1];
+        v[i] = a0 * c[i] + a1 * s[i + 1];
+        v[i + 1] = a1 * c[i + 1] - a0 * s[i];
+    }
+}
+__device__ __forceinline__ void ldf8(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// Sixteen lanes per (token, head) item, 16-byte accesses, two items per warp and two such pairs per iteration: every
+// lane keeps six 16-byte loads in flight.  (With one warp per item and 8-byte accesses the kernel reached 0.6 of the
+// copy bandwidth forward and 0.3 backward.)
+__global__ void __launch_bounds__(256, 3) qkv_post_fwd_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q,
     __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v, long rows, int heads, long seq_in, long seq_out,
     long out_offset, long rope_len, float eps) {
-    const int lane = threadIdx.x & 31;
+    constexpr int U = 2;
+    const int lane = threadIdx.x & 31, sub = lane >> 4, l = lane & 15;
     const long nwork = rows * heads;
-    const long stride = (long)gridDim.x * (blockDim.x >> 5);
-    float wq[4], wk[4];
-    ld4(qw + lane * 4, wq);
-    ld4(kw + lane * 4, wk);
-    for (long w = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < nwork; w += stride) {
-        const long row = w / heads;
-        const int h = (int)(w - row * heads);
-        const long b = row / seq_in, s = row - b * seq_in;
-        const __nv_bfloat16* src = qkv + (row * heads + h) * (3L * D) + lane * 4;
-        const long dst = ((b * heads + h) * seq_out + out_offset + s) * D + lane * 4;
-        float xq[4], xk[4];
-        ld4(src, xq);
-        ld4(src + D, xk);
-        // v: plain copy
-        *reinterpret_cast<uint2*>(v + dst) = *reinterpret_cast<const uint2*>(src + 2 * D);
-        float sq = xq[0] * xq[0] + xq[1] * xq[1] + xq[2] * xq[2] + xq[3] * xq[3];
-        float sk = xk[0] * xk[0] + xk[1] * xk[1] + xk[2] * xk[2] + xk[3] * xk[3];
-        const float rq = rsqrtf(warp_sum(sq) * (1.f / D) + eps);
-        const float rk = rsqrtf(warp_sum(sk) * (1.f / D) + eps);
-        float nq[4], nk[4];
+    const long warp_id = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long stride = (long)gridDim.x * (blockDim.x >> 5) * (2 * U);
+    float wq[8], wk[8];
+    unpack8(ld8(qw + l * 8), wq);
+    unpack8(ld8(kw + l * 8), wk);
+    for (long w0 = warp_id * (2 * U); w0 < nwork; w0 += stride) {
+        bf16x8 pq[U], pk[U], pv[U];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            // the reference rounds the normalised value to bf16 before the rotation; keep fp32 instead
-            nq[j] = xq[j] * rq * wq[j];
-            nk[j] = xk[j] * rk * wk[j];
+        for (int u = 0; u < U; ++u) {
+            const long w = w0 + u * 2 + sub;
+            if (w < nwork) {
+                const __nv_bfloat16* src = qkv + w * (3L * D) + l * 8;
+                pq[u] = ld8(src);
+                pk[u] = ld8(src + D);
+                pv[u] = ld8(src + 2 * D);
+            } else {
+                pq[u] = pk[u] = pv[u] = bf16x8{};
+            }
         }
-        if (s < rope_len) {
-            const float4 c = *reinterpret_cast<const float4*>(cos_t + s * D + lane * 4);
-            const float4 sn = *reinterpret_cast<const float4*>(sin_t + s * D + lane * 4);
-            float oq[4], ok[4];
-            oq[0] = nq[0] * c.x - nq[1] * sn.x;
-            oq[1] = nq[1] * c.y + nq[0] * sn.y;
-            oq[2] = nq[2] * c.z - nq[3] * sn.z;
-            oq[3] = nq[3] * c.w + nq[2] * sn.w;
-            ok[0] = nk[0] * c.x - nk[1] * sn.x;
-            ok[1] = nk[1] * c.y + nk[0] * sn.y;
-            ok[2] = nk[2] * c.z - nk[3] * sn.z;
-            ok[3] = nk[3] * c.w + nk[2] * sn.w;
-            st4(q + dst, oq);
-            st4(k + dst, ok);
-        } else {
-            st4(q + dst, nq);
-            st4(k + dst, nk);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long w = w0 + u * 2 + sub;
+            const bool ok = w < nwork;
+            const long row = ok ? w / heads : 0;
+            const int h = ok ? (int)(w - row * heads) : 0;
+            const long b = row / seq_in, s = row - b * seq_in;
+            const long dst = ((b * heads + h) * seq_out + out_offset + s) * D + l * 8;
+            float xq[8], xk[8];
+            unpack8(pq[u], xq);
+            unpack8(pk[u], xk);
+            float sq = 0.f, sk = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                sq += xq[j] * xq[j];
+                sk += xk[j] * xk[j];
+            }
+            const float rq = rsqrtf(half_warp_sum(sq) * (1.f / D) + eps);
+            const float rk = rsqrtf(half_warp_sum(sk) * (1.f / D) + eps);
+            if (ok) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // the reference rounds the normalised value to bf16 before the rotation; keep fp32 instead
+                    xq[j] *= rq * wq[j];
+                    xk[j] *= rk * wk[j];
+                }
+                if (s < rope_len) {
+                    float c[8], sn[8];
+                    ldf8(cos_t + s * D + l * 8, c);
+                    ldf8(sin_t + s * D + l * 8, sn);
+                    rope8(xq, c, sn);
+                    rope8(xk, c, sn);
+                }
+                st8(q + dst, pack8(xq));
+                st8(k + dst, pack8(xk));
+                st8(v + dst, pv[u]);
+            }
         }
     }
 }
@@ -97,86 +143,111 @@ struct PeerTable3 {
 // partials: [gridDim.x * warps][2][128] fp32 (dq-norm weight, dk-norm weight)
 // dq / dk / dv live head-sharded on the rank that owns each head ([batch, heads_per_rank, seq_out, 128]); with
 // more than one rank this kernel reads them over NVLink, which is the head -> sequence all-to-all of the
-// Ulysses backward fused with the RoPE transpose and the RMSNorm backward.
-__global__ void __launch_bounds__(256) qkv_post_bwd_kernel(
+// Ulysses backward fused with the RoPE transpose and the RMSNorm backward.  Same lane layout as the forward kernel:
+// sixteen lanes per (token, head) item, whole 256-byte rows per half-warp on the peer side.
+__global__ void __launch_bounds__(256, 3) qkv_post_bwd_kernel(
     const PeerTable3 src, const int heads_per_rank, const __nv_bfloat16* __restrict__ qkv,
     const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ dqkv,
     float* __restrict__ partials, long rows, int heads, long seq_in, long seq_out, long out_offset, long rope_len,
     float eps) {
-    const int lane = threadIdx.x & 31;
+    constexpr int U = 1;      // with two items per lane the kernel needed 156 registers: one CTA per SM
+    const int lane = threadIdx.x & 31, sub = lane >> 4, l = lane & 15;
     const long nwork = rows * heads;
     const long gw = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long stride = (long)gridDim.x * (blockDim.x >> 5);
-    float wq[4], wk[4], aq[4] = {0.f, 0.f, 0.f, 0.f}, ak[4] = {0.f, 0.f, 0.f, 0.f};
-    ld4(qw + lane * 4, wq);
-    ld4(kw + lane * 4, wk);
-    for (long w = gw; w < nwork; w += stride) {
-        const long row = w / heads;
-        const int h = (int)(w - row * heads);
-        const long b = row / seq_in, s = row - b * seq_in;
-        const long off_in = (row * heads + h) * (3L * D) + lane * 4;
-        const int owner = h / heads_per_rank, hl = h - owner * heads_per_rank;
-        const long so = ((b * heads_per_rank + hl) * seq_out + out_offset + s) * D + lane * 4;
-        float gq[4], gk[4], xq[4], xk[4];
-        ld4(src.q[owner] + so, gq);
-        ld4(src.k[owner] + so, gk);
-        ld4(qkv + off_in, xq);
-        ld4(qkv + off_in + D, xk);
-        *reinterpret_cast<uint2*>(dqkv + off_in + 2 * D) = *reinterpret_cast<const uint2*>(src.v[owner] + so);
-        if (s < rope_len) {        // transpose of the rotation
-            const float4 c = *reinterpret_cast<const float4*>(cos_t + s * D + lane * 4);
-            const float4 sn = *reinterpret_cast<const float4*>(sin_t + s * D + lane * 4);
-            float t[4];
-            t[0] = gq[0] * c.x + gq[1] * sn.y;
-            t[1] = gq[1] * c.y - gq[0] * sn.x;
-            t[2] = gq[2] * c.z + gq[3] * sn.w;
-            t[3] = gq[3] * c.w - gq[2] * sn.z;
+    const long stride = (long)gridDim.x * (blockDim.x >> 5) * (2 * U);
+    float wq[8], wk[8], aq[8], ak[8];
+    unpack8(ld8(qw + l * 8), wq);
+    unpack8(ld8(kw + l * 8), wk);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) gq[j] = t[j];
-            t[0] = gk[0] * c.x + gk[1] * sn.y;
-            t[1] = gk[1] * c.y - gk[0] * sn.x;
-            t[2] = gk[2] * c.z + gk[3] * sn.w;
-            t[3] = gk[3] * c.w - gk[2] * sn.z;
+    for (int j = 0; j < 8; ++j) aq[j] = ak[j] = 0.f;
+    for (long w0 = gw * (2 * U); w0 < nwork; w0 += stride) {
+        bf16x8 pgq[U], pgk[U], pgv[U], pxq[U], pxk[U];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) gk[j] = t[j];
+        for (int u = 0; u < U; ++u) {
+            const long w = w0 + u * 2 + sub;
+            if (w < nwork) {
+                const long row = w / heads;
+                const int h = (int)(w - row * heads);
+                const long b = row / seq_in, s = row - b * seq_in;
+                const int owner = h / heads_per_rank, hl = h - owner * heads_per_rank;
+                const long so = ((b * heads_per_rank + hl) * seq_out + out_offset + s) * D + l * 8;
+                pgq[u] = ld8(src.q[owner] + so);
+                pgk[u] = ld8(src.k[owner] + so);
+                pgv[u] = ld8(src.v[owner] + so);
+                pxq[u] = ld8(qkv + w * (3L * D) + l * 8);
+                pxk[u] = ld8(qkv + w * (3L * D) + D + l * 8);
+            } else {
+                pgq[u] = pgk[u] = pgv[u] = pxq[u] = pxk[u] = bf16x8{};
+            }
         }
-        float sq = 0.f, sk = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            sq += xq[j] * xq[j];
-            sk += xk[j] * xk[j];
-        }
-        const float rq = rsqrtf(warp_sum(sq) * (1.f / D) + eps);
-        const float rk = rsqrtf(warp_sum(sk) * (1.f / D) + eps);
-        float hq[4], hk[4], cq = 0.f, ck = 0.f;
+        for (int u = 0; u < U; ++u) {
+            const long w = w0 + u * 2 + sub;
+            const bool ok = w < nwork;
+            const long row = ok ? w / heads : 0;
+            const long b = row / seq_in, s = row - b * seq_in;
+            float gq[8], gk[8], xq[8], xk[8];
+            unpack8(pgq[u], gq);
+            unpack8(pgk[u], gk);
+            unpack8(pxq[u], xq);
+            unpack8(pxk[u], xk);
+            if (ok && s < rope_len) {        // transpose of the rotation
+                float c[8], sn[8];
+                ldf8(cos_t + s * D + l * 8, c);
+                ldf8(sin_t + s * D + l * 8, sn);
+                rope8_transpose(gq, c, sn);
+                rope8_transpose(gk, c, sn);
+            }
+            float sq = 0.f, sk = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            hq[j] = xq[j] * rq;
-            hk[j] = xk[j] * rk;
-            aq[j] += gq[j] * hq[j];
-            ak[j] += gk[j] * hk[j];
-            gq[j] *= wq[j];
-            gk[j] *= wk[j];
-            cq += gq[j] * hq[j];
-            ck += gk[j] * hk[j];
-        }
-        cq = warp_sum(cq) * (1.f / D);
-        ck = warp_sum(ck) * (1.f / D);
-        float oq[4], ok[4];
+            for (int j = 0; j < 8; ++j) {
+                sq += xq[j] * xq[j];
+                sk += xk[j] * xk[j];
+            }
+            const float rq = rsqrtf(half_warp_sum(sq) * (1.f / D) + eps);
+            const float rk = rsqrtf(half_warp_sum(sk) * (1.f / D) + eps);
+            float cq = 0.f, ck = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            oq[j] = rq * (gq[j] - hq[j] * cq);
-            ok[j] = rk * (gk[j] - hk[j] * ck);
+            for (int j = 0; j < 8; ++j) {
+                xq[j] *= rq;                 // x_hat
+                xk[j] *= rk;
+                aq[j] += gq[j] * xq[j];
+                ak[j] += gk[j] * xk[j];
+                gq[j] *= wq[j];
+                gk[j] *= wk[j];
+                cq += gq[j] * xq[j];
+                ck += gk[j] * xk[j];
+            }
+            cq = half_warp_sum(cq) * (1.f / D);
+            ck = half_warp_sum(ck) * (1.f / D);
+            if (ok) {
+                float oq[8], okk[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    oq[j] = rq * (gq[j] - xq[j] * cq);
+                    okk[j] = rk * (gk[j] - xk[j] * ck);
+                }
+                __nv_bfloat16* dst = dqkv + w * (3L * D) + l * 8;
+                st8(dst, pack8(oq));
+                st8(dst + D, pack8(okk));
+                st8(dst + 2 * D, pgv[u]);
+            }
         }
-        st4(dqkv + off_in, oq);
-        st4(dqkv + off_in + D, ok);
     }
-    float* p = partials + gw * (2L * D) + lane * 4;
+    // the two halves of the warp own the same columns
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        p[j] = aq[j];
-        p[D + j] = ak[j];
+    for (int j = 0; j < 8; ++j) {
+        aq[j] += __shfl_xor_sync(0xffffffffu, aq[j], 16);
+        ak[j] += __shfl_xor_sync(0xffffffffu, ak[j], 16);
+    }
+    if (sub == 0) {
+        float* p = partials + gw * (2L * D) + l * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            p[j] = aq[j];
+            p[D + j] = ak[j];
+        }
     }
 }
 

@@ -8,7 +8,8 @@ the CFG-zero-star rescaling (``:954-969``), embedded guidance, VAE decode (``:10
 
 It is an ``nn.Module``-free orchestrator over components that this package owns: the transformer, the VAE and the
 two text encoders (:mod:`teletron_b200.models`).  Frames come back as a ``[B, F, 3, H, W]`` tensor in ``[0, 1]``;
-:func:`save_video_tensor` writes them as ``.pt`` / ``.npy`` (no video-container writer is bundled).
+:func:`save_video_tensor` writes them as a video file (:mod:`teletron_b200.inference.video_io`: ``.avi`` with no
+dependency, ``.mp4`` through OpenCV, ``.gif``) or as ``.pt`` / ``.npy``.
 """
 
 from __future__ import annotations
@@ -51,12 +52,10 @@ def flow_sigmas(num_steps: int, shift: float = 7.0, device=None) -> torch.Tensor
     return shift * s / (1 + (shift - 1) * s)
 
 
-def save_video_tensor(frames: torch.Tensor, path: str) -> None:
-    if path.endswith(".npy"):
-        import numpy as np
-        np.save(path, (frames.clamp(0, 1) * 255).round().to(torch.uint8).cpu().numpy())
-    else:
-        torch.save(frames.cpu(), path)
+def save_video_tensor(frames: torch.Tensor, path: str, fps: float = 15.0) -> str:
+    """``frames [F, 3, H, W]`` in ``[0, 1]`` -> file chosen by the extension; returns the path written."""
+    from .video_io import export_to_video
+    return export_to_video(frames, path, fps)
 
 
 class HunyuanVideoPipeline:

@@ -31,6 +31,12 @@ def strict() -> bool:
     return _STRICT
 
 
+def vector_shaped(*dims: int) -> bool:
+    """A product with a dimension below 8 (the modulation vectors: batch-1 GEMV, rank-1 weight gradients) has no tile
+    for the tensor-core kernel and is not what the policy is about; such cases go to the library without a note."""
+    return min(dims) < 8
+
+
 def note(site: str, detail: str) -> None:
     key = f"{site}: {detail}"
     n = SEEN.get(key, 0)

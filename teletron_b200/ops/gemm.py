@@ -43,7 +43,8 @@ def _native(a: torch.Tensor, b: torch.Tensor, layout: str, bias: Optional[torch.
             raise RuntimeError(f"tcgen05 GEMM does not take {layout} {tuple(a.shape)} x {tuple(b.shape)}")
         if a.is_cuda and a.dtype == torch.bfloat16:
             from . import fallback
-            fallback.note("gemm", f"{layout} {tuple(a.shape)} x {tuple(b.shape)} strides {a.stride()} {b.stride()}")
+            if not fallback.vector_shaped(*a.shape, *b.shape):
+                fallback.note("gemm", f"{layout} {tuple(a.shape)} x {tuple(b.shape)} strides {a.stride()} {b.stride()}")
         return None
     COUNTERS["tcgen05"] += 1
     return gemm_tcgen05.gemm(a, b, layout, bias)
@@ -83,7 +84,8 @@ def gemm_tn_into(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.T
             return out
     if _BACKEND != "cublas" and a.is_cuda and a.dtype == torch.bfloat16:
         from . import fallback
-        fallback.note("gemm", f"tn-into {tuple(a.shape)} x {tuple(b.shape)} out strides {out.stride()}")
+        if not fallback.vector_shaped(*a.shape, *b.shape):
+            fallback.note("gemm", f"tn-into {tuple(a.shape)} x {tuple(b.shape)} out strides {out.stride()}")
     COUNTERS["cublas"] += 1
     torch.matmul(a.t(), b, out=out) if out.is_contiguous() else out.copy_(torch.matmul(a.t(), b))
     return out

@@ -78,6 +78,9 @@ def _add_parallel_args(p):
     g = p.add_argument_group("parallelism")
     g.add_argument("--tensor-model-parallel-size", type=int, default=1)
     g.add_argument("--pipeline-model-parallel-size", type=int, default=1)
+    g.add_argument("--virtual-pipeline-model-parallel-size", type=int, default=None)
+    g.add_argument("--expert-model-parallel-size", type=int, default=1,
+                   help="builds the expert-parallel groups inside data parallelism (the DiT has no expert layers)")
     g.add_argument("--context-parallel-size", type=int, default=1)
     g.add_argument("--sequence-pad-multiple", type=int, default=8,
                    help="pad every context-parallel chunk of video tokens to a multiple of this (keeps weight-gradient GEMMs on the tensor-core kernel)")
@@ -103,8 +106,11 @@ def _add_parallel_args(p):
     g.add_argument("--encoder-text-dim", type=int, default=None)
     g.add_argument("--encoder-pooled-dim", type=int, default=None)
     g.add_argument("--encoder-max-text-len", type=int, default=256)
-    g.add_argument("--nccl-communicator-config-path", type=str, default=None)
-    g.add_argument("--tp-comm-overlap", action="store_true")
+    g.add_argument("--nccl-communicator-config-path", type=str, default=None,
+                   help="YAML file {group kind: {cga_cluster_size, max_ctas, min_ctas}} applied to the NCCL communicators of those groups")
+    g.add_argument("--tp-comm-overlap", action="store_true",
+                   help="overlap tensor-parallel communication with the GEMMs: here that is the sequence-parallel layout with the "
+                        "all-gather -> GEMM / GEMM -> reduce-scatter kernels, so the flag turns on --sequence-parallel and --fused-comm")
     g.add_argument("--local-rank", "--local_rank", type=int, default=None)
 
 
@@ -193,6 +199,9 @@ def validate_args(args, world_size: Optional[int] = None):
     if args.pipeline_model_parallel_size != 1:
         raise ValueError("pipeline parallelism is not supported by this model (the reference builds the "
                          "groups but every rank owns all blocks, pipeline.py:239-240)")
+    if args.tp_comm_overlap and args.tensor_model_parallel_size > 1:
+        args.sequence_parallel = True
+        args.fused_comm = True
     mp = args.tensor_model_parallel_size * args.context_parallel_size
     if args.dit_world_size % mp:
         raise ValueError(f"DiT world size {args.dit_world_size} not divisible by tp*cp={mp}")

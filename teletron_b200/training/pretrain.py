@@ -85,7 +85,11 @@ def initialize(extra_args_provider: Optional[Callable] = None, argv=None, args_d
                                 timeout=datetime.timedelta(minutes=args.distributed_timeout_minutes), **kw)
     enc = args.distributed_vae_world_size if args.distributed_vae else 0
     ps.initialize_model_parallel(args.tensor_model_parallel_size, args.context_parallel_size, enc,
-                                 timeout_minutes=args.distributed_timeout_minutes)
+                                 timeout_minutes=args.distributed_timeout_minutes,
+                                 pipeline_model_parallel_size=args.pipeline_model_parallel_size,
+                                 virtual_pipeline_model_parallel_size=args.virtual_pipeline_model_parallel_size,
+                                 expert_model_parallel_size=args.expert_model_parallel_size,
+                                 nccl_communicator_config_path=args.nccl_communicator_config_path)
     if ps.is_dit_rank():
         set_random_seed(args.seed, args.data_parallel_random_init)
     if use_cuda:
