@@ -58,8 +58,10 @@ def parse():
                         "every native call and NCCL section) and write the table to this file")
     p.add_argument("--overlap-grad-reduce", type=int, default=0,
                    help="1: bucketed gradient reduce-scatter on a side stream during backward")
-    p.add_argument("--sequence-parallel", type=int, default=0,
-                   help="1: shard the residual stream's tokens over the tensor-parallel ranks (all-gather -> GEMM / GEMM -> reduce-scatter)")
+    p.add_argument("--sequence-parallel", type=int, default=None,
+                   help="1: shard the residual stream's tokens over the tensor-parallel ranks, MLPs on the fused all-gather -> GEMM / "
+                        "GEMM -> reduce-scatter kernels; 0: replicated activations with NCCL all-reduce.  Default: 1 whenever tp > 1 "
+                        "and the fused collectives are on")
     return p.parse_args()
 
 
@@ -139,10 +141,14 @@ def run_breakdown(step_fn, dev):
     if dist.is_initialized():
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    from teletron_b200.ops import status as _status
     _lib.profile_start()
+    t_host0 = time.perf_counter()
     e0.record()
     step_fn()
     e1.record()
+    # host time to enqueue forward + backward + gradient sync: up to the status check, the first point where the host waits
+    host_enqueue_ms = (_status.LAST_CHECK_HOST_TIME - t_host0) * 1e3
     prof = _lib.profile_stop()
     step_ms = e0.elapsed_time(e1)
     names = sorted(prof)
@@ -151,7 +157,7 @@ def run_breakdown(step_fn, dev):
     if dist.is_initialized():
         # the ranks run the same program, so the same names in the same order
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    return {"step_ms": float(mine[-1]), "step_ms_max": float(worst[-1]),
+    return {"step_ms": float(mine[-1]), "step_ms_max": float(worst[-1]), "host_enqueue_ms": host_enqueue_ms,
             "phases": {n: (prof[n][0], prof[n][1], float(worst[i])) for i, n in enumerate(names)}}
 
 
@@ -184,7 +190,8 @@ def format_breakdown(b, line) -> str:
     total = sum(r[1] for r in rows)
     out = [f"per-phase device time of one training step (CUDA events around every native call / NCCL section; rank 0 and max over ranks)",
            f"config: {json.dumps(line['config'])}",
-           f"step: {b['step_ms']:.1f} ms on rank 0 ({b['step_ms_max']:.1f} ms max over ranks); timed loop: {line['ms_per_step']:.1f} ms/step",
+           f"step: {b['step_ms']:.1f} ms on rank 0 ({b['step_ms_max']:.1f} ms max over ranks); timed loop: {line['ms_per_step']:.1f} ms/step; "
+           f"host needed {b['host_enqueue_ms']:.1f} ms to enqueue forward + backward + gradient sync (with the profiling events)",
            f"{'phase':<72}{'ms':>10}{'share':>8}{'calls':>8}{'max ms':>10}"]
     for title, ms, n, mx in sorted(rows, key=lambda r: -r[1]):
         out.append(f"{title:<72}{ms:>10.2f}{100 * ms / b['step_ms']:>7.1f}%{n:>8d}{mx:>10.2f}")
@@ -240,6 +247,8 @@ def main():
         argv += ["--fused-comm"]
     if a.overlap_grad_reduce and a.gpus > 1:
         argv += ["--overlap-grad-reduce"]
+    if a.sequence_parallel is None:
+        a.sequence_parallel = 1 if (a.impl == "ours" and a.fused_comm) else 0
     sp = bool(a.sequence_parallel) and tp > 1
     if sp:
         argv += ["--sequence-parallel"]

@@ -64,7 +64,16 @@ struct BwdParams {
     int* status;
     const __nv_bfloat16* q_raw;     // q [BH, S, 128] and dout [B, S, H * 128] as plain pointers: the variant that keeps the
     const __nv_bfloat16* do_raw;    // stationary operands in tensor memory loads them with ordinary loads
+#ifdef TT_ATTN_STAMPS
+    long long* stamps;              // scratch builds only: clock64() of CTA (0, 0)'s pipeline events, [chunk][10]
+#endif
 };
+
+#ifdef TT_ATTN_STAMPS
+#define TT_STAMP(slot) do { if (p.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && c < 256) p.stamps[c * 10 + (slot)] = clock64(); } while (0)
+#else
+#define TT_STAMP(slot) do { } while (0)
+#endif
 
 // delta[bh, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head)
 __global__ void __launch_bounds__(256) delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
@@ -226,7 +235,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const uint32_t par = (uint32_t)c & 1u;
                 const bool more = c + 1 < n_chunks;
                 // T1 is free as soon as every softmax warp has read S(c): the next chunk's scores overlap the dS pass
+                TT_STAMP(0);
                 if (!mbar_wait(p_ready, par, &abort_flag)) goto done;
+                TT_STAMP(1);
                 tc_fence_after();
                 if (more) {
                     const int n1 = (c + 1) % kRing1;
@@ -235,13 +246,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     issue_t(kT1, sA1, sRing1 + n1 * kTile);
                     umma_commit(s_full);
                 }
+                TT_STAMP(2);
                 // T2 now holds bf16 P (first 16 columns of every 32) and dS (last 16) of this chunk
                 if (!mbar_wait(ds_ready, par, &abort_flag)) goto done;
+                TT_STAMP(3);
                 tc_fence_after();
                 issue_acc(KVS ? kAcc2 : kAcc1, kT2 + 16, sRing1 + (c % kRing1) * kTile, c == 0);   // dK += dS^T Q  /  dQ += dS K
                 umma_commit(b1_empty(c % kRing1));
                 if (KVS) issue_acc(kAcc1, kT2, sRing2 + (c % kRing2) * kTile, c == 0);             // dV += P^T dO
                 umma_commit(b2_empty(c % kRing2));
+                TT_STAMP(4);
                 if (more) {
                     const int n2 = (c + 1) % kRing2;
                     if (!mbar_wait(b2_full(n2), (uint32_t)((c + 1) / kRing2) & 1u, &abort_flag)) goto done;
@@ -249,6 +263,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     issue_t(kT2, sA2, sRing2 + n2 * kTile);                                        // next chunk's dP
                     umma_commit(dp_full);
                 }
+                TT_STAMP(5);
             }
             umma_commit(acc_final);
         }
@@ -317,6 +332,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                              (p.mask_lo >= p.mask_hi || p.mask_hi <= c * BC || p.mask_lo >= (c + 1) * BC));
 #endif
             if (!mbar_wait(s_full, par, &abort_flag)) goto done;
+            if (threadIdx.x == 64) TT_STAMP(6);
             tc_fence_after();
             {
                 constexpr int pass = 0;
@@ -361,8 +377,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
+            if (threadIdx.x == 64) TT_STAMP(7);
 
             if (!mbar_wait(dp_full, par, &abort_flag)) goto done;
+            if (threadIdx.x == 64) TT_STAMP(8);
             tc_fence_after();
             uint32_t dk[16];
             {
@@ -399,6 +417,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_ready);
+            if (threadIdx.x == 64) TT_STAMP(9);
         }
         // ------------------------------------------------------------ epilogue
         if (!mbar_wait(acc_final, 0, &abort_flag)) goto done;
@@ -446,6 +465,11 @@ done:
 
 // lse, delta: [B*H, pitch] fp32 with pitch a multiple of 64; lse holds +inf and delta 0 at positions >= S
 // (delta is scratch owned by the caller, zero-initialised; this call fills positions < S).
+#ifdef TT_ATTN_STAMPS
+static long long* g_attn_stamps = nullptr;
+extern "C" void tt_attn_set_stamps(long long* ptr) { g_attn_stamps = ptr; }
+#endif
+
 extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                            const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len,
                            int mask_lo, int mask_hi, int pitch, float scale, int* status, void* stream) {
@@ -460,7 +484,10 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     if ((rc = tt_make_tmap_3d(&tk_s, k, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_3d(&tv_s, v, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_bshd(&tdo_s, dout, (uint64_t)B, (uint64_t)S, (uint64_t)H, BS)) != TT_OK) return rc;
-    static bool configured = false;
+    static bool configured_dev[64] = {false};   // per device: the attribute belongs to the device's context
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    bool& configured = configured_dev[dev];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e == cudaSuccess)
@@ -488,6 +515,9 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     p.status = status;
     p.q_raw = (const __nv_bfloat16*)q;
     p.do_raw = (const __nv_bfloat16*)dout;
+#ifdef TT_ATTN_STAMPS
+    p.stamps = g_attn_stamps;
+#endif
     // dK, dV: stationary keys (K, V resident), streamed queries (Q, dO)
     p.out1 = (__nv_bfloat16*)dv;
     p.out2 = (__nv_bfloat16*)dk;
@@ -496,6 +526,9 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     // dQ: stationary queries (Q, dO resident), streamed keys (K, V)
     p.out1 = (__nv_bfloat16*)dq;
     p.out2 = nullptr;
+#ifdef TT_ATTN_STAMPS
+    if (p.stamps != nullptr) p.stamps += 2560;      // second half of the buffer: the query-stationary kernel
+#endif
     // TELETRON_B200_ATTN_BWD_TSA=1 selects the variant with Q / dO in tensor memory (off by default)
     static const bool tsa = [] { const char* v = getenv("TELETRON_B200_ATTN_BWD_TSA"); return v != nullptr && v[0] == '1'; }();
     if (tsa)

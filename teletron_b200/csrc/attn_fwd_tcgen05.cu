@@ -374,11 +374,13 @@ static int attn_fwd_launch(const void* q, const void* k, const void* v, void* ou
     if ((rc = tt_make_tmap_3d(&tq, q, BH, (uint64_t)S, D, D, (uint64_t)S * D, BQ, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_3d(&tk, k, BH, (uint64_t)S, D, D, (uint64_t)S * D, BKV, 64)) != TT_OK) return rc;
     if ((rc = tt_make_tmap_3d(&tv, v, BH, (uint64_t)S, D, D, (uint64_t)S * D, BKV, 64)) != TT_OK) return rc;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};       // per device: the attribute belongs to the device's context
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return tt_record_cuda(e);
-        configured = true;
+        configured[dev] = true;
     }
     AttnParams p;
     p.out = (__nv_bfloat16*)out;

@@ -548,11 +548,14 @@ int launch(const TmapArray& tmA, const CUtensorMap& tmB, const GemmParams& p, in
     // staging for the coalesced peer stores (4 epilogue warps x 8 KB), only when that variant is selected
     const bool staged_stores = EPI == 6 || EPI == 5;
     const int smem = C::kSmemBytes + (staged_stores ? 4 * 8192 : 0);
-    static int configured = 0;
-    if (configured < smem) {
+    // the attribute belongs to the device's context: remembered per device, not per process
+    static int configured[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (configured[dev] < smem) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return tt_record_cuda(e);
-        configured = smem;
+        configured[dev] = smem;
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;

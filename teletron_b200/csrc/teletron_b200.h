@@ -56,6 +56,13 @@ int tt_qkv_post_bwd_peer(void* const* dq_ptrs, void* const* dk_ptrs, void* const
 int tt_gelu_fwd(const void* u, void* y, long n, int kind, void* stream);   /* kind 0 = erf, 1 = tanh */
 int tt_gelu_bwd(const void* dy, const void* u, void* du, long n, int kind, void* stream);
 
+/* ---- flow matching: noise mix and weighted MSE loss (+ its gradient) ---- */
+int tt_flow_loss_blocks(void);
+int tt_noise_mix(const void* latents, const void* noise, const float* sigma, void* out, long n_per_batch, int batch,
+                 void* stream);
+int tt_flow_loss(const void* pred, const void* noise, const void* latents, const float* weight, float* partials,
+                 void* dpred, float* loss, long n_per_batch, int batch, void* stream);
+
 /* ---- optimizer ---- */
 int tt_adamw(void* param, const void* grad, void* m, void* v, float* master, void* master_lo, long n,
              int state_is_bf16, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale,

@@ -239,11 +239,9 @@ def _ulysses_attention(q, k, v, tq, tk, tv, pad: Optional[SeqPad], kv_valid_len:
 
 
 _FUSED_COMM = False
-# Collective workspaces (symmetric heaps) by shape key, least recently used first.  Training uses one or two shapes; data with
-# varying clip lengths would otherwise keep a heap per length for ever, so the cache is bounded: when a new shape arrives
-# and the cache is full, the least recently used workspace is closed after a device synchronisation.  Every rank of a group
-# sees the same sequence of shapes, so all of them evict the same entry.  The bound must exceed the number of distinct
-# shapes alive inside one training step (their buffers back tensors saved for backward).
+# Collective workspaces (symmetric heaps) by kind, least recently used first.  One workspace per kind serves every clip
+# length (it is re-laid-out in place, see _workspace); the cache bound only matters for models with several head counts or
+# widths.  Every rank of a group sees the same sequence of shapes, so all of them make the same decisions.
 _WORKSPACES = collections.OrderedDict()
 _MAX_WORKSPACES = int(os.environ.get("TELETRON_B200_MAX_WORKSPACES", "8"))
 
@@ -290,15 +288,45 @@ def _use_fused_tp(x: torch.Tensor, sequence_parallel: bool, activation) -> bool:
             and ps.group_is_single_node(ps.get_tensor_model_parallel_group()))
 
 
+# Collective workspaces are sized with head-room (TELETRON_B200_WORKSPACE_HEADROOM, default 1.0 = exactly the first shape)
+# and re-laid-out in place when the clip length changes; only a sequence longer than everything seen before makes every
+# rank close the slab (collectively) and allocate a larger one.
+_HEADROOM = float(os.environ.get("TELETRON_B200_WORKSPACE_HEADROOM", "1.0"))
+
+
 def _tp_workspace(rows: int, k_max: int, n_max: int):
     from ...ops.fused_comm import TPWorkspace
     width = max(k_max, n_max)
-    return _cached_workspace(("tp", rows, width), lambda: TPWorkspace(ps.get_tensor_model_parallel_group(), rows, width, width))
+    key = ("tp", width)
+    ws = _WORKSPACES.get(key)
+    if ws is not None and not ws.fits(rows):
+        del _WORKSPACES[key]
+        ws.heap.close(collective=True)
+        ws = None
+    if ws is None:
+        ws = _cached_workspace(key, lambda: TPWorkspace(ps.get_tensor_model_parallel_group(), rows, width, width,
+                                                        capacity_rows=int(rows * _HEADROOM)))
+    elif ws.rows != rows:
+        ws.configure(rows)
+    return _cached_workspace(key, lambda: ws)
 
 
 def _workspace(heads_local: int, s: int, T: int):
     from ...ops.fused_comm import UlyssesWorkspace
-    return _cached_workspace((heads_local, s, T), lambda: UlyssesWorkspace(ps.get_context_parallel_group(), heads_local, s, T))
+    key = ("ulysses", heads_local)
+    ws = _WORKSPACES.get(key)
+    if ws is not None and not ws.fits(s, T):
+        del _WORKSPACES[key]
+        ws.heap.close(collective=True)
+        ws = None
+    if ws is None:
+        group = ps.get_context_parallel_group()
+        cp = ps.get_context_parallel_world_size()
+        cap = int(UlyssesWorkspace.bytes_needed(heads_local, cp, s, T) * _HEADROOM)
+        ws = _cached_workspace(key, lambda: UlyssesWorkspace(group, heads_local, s, T, capacity_bytes=cap))
+    elif (ws.s, ws.T) != (s, T):
+        ws.configure(s, T)
+    return _cached_workspace(key, lambda: ws)
 
 
 def _fused_kv_len(ws, pad: Optional[SeqPad], kv_valid_len):

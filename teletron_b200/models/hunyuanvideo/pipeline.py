@@ -136,8 +136,7 @@ class HunyuanPipeline(nn.Module):
             B = latents.shape[0]
             sigma, noise = self._draw(B, latents.shape, dev, dtype)
             timesteps = (sigma * self.scheduler.num_train_timesteps).long()
-            sig = sigma.view(B, 1, 1, 1, 1).to(dtype)
-            noisy = (1.0 - sig) * latents + sig * noise
+            noisy = ops.noise_mix(latents, noise, sigma)
 
             if flow.model_type == "i2v":
                 if batch.get("first_frame_latents") is not None:

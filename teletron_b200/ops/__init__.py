@@ -161,5 +161,22 @@ def joint_qkv_projection(x, weight, bias, q_norm_weight, k_norm_weight, cos, sin
                                           bias2, q_norm_weight2, k_norm_weight2, num_heads, eps)
 
 
+def _flow_kernel_ok(*tensors) -> bool:
+    t0 = tensors[0]
+    return (t0.is_cuda and all(t.dtype == torch.bfloat16 and t.shape == t0.shape for t in tensors)
+            and (t0.numel() // max(1, t0.shape[0])) % 8 == 0 and _use_cuda(t0))
+
+
 def flow_match_loss(pred, noise, latents, weight):
+    if _flow_kernel_ok(pred, noise, latents):
+        from . import cuda_ops
+        return cuda_ops.flow_match_loss(pred, noise, latents, weight)
     return reference.flow_match_loss(pred, noise, latents, weight)
+
+
+def noise_mix(latents, noise, sigma):
+    """Model input of a flow-matching step: ``(1 - sigma) * latents + sigma * noise`` with one noise level per sample."""
+    if _flow_kernel_ok(latents, noise):
+        from . import cuda_ops
+        return cuda_ops.noise_mix(latents, noise, sigma)
+    return reference.noise_mix(latents, noise, sigma)

@@ -340,6 +340,53 @@ def attention(q, k, v, kv_valid_len=None, scale=None, mask_range=None):
 
 
 # ---------------------------------------------------------------------------------------------
+# flow matching: noise mix and weighted MSE loss
+# ---------------------------------------------------------------------------------------------
+
+def noise_mix(latents: torch.Tensor, noise: torch.Tensor, sigma: torch.Tensor) -> torch.Tensor:
+    """``(1 - sigma[b]) * latents + sigma[b] * noise`` in one pass (no gradient: the inputs are data)."""
+    B = latents.shape[0]
+    lat = check(latents.contiguous(), BF16, "latents")
+    nz = check(noise.contiguous(), BF16, "noise")
+    sg = check(sigma.float().contiguous(), torch.float32, "sigma", align=4)
+    out = torch.empty_like(lat)
+    call("tt_noise_mix", ptr(lat), ptr(nz), ptr(sg), ptr(out), c_long(lat.numel() // B), c_int(B), stream())
+    return out
+
+
+class _FlowMatchLoss(torch.autograd.Function):
+    """``mean(weight[b] * (pred - (noise - latents))^2)``: the forward kernel also writes d loss / d pred, so the backward is
+    one scaling by the incoming scalar."""
+
+    @staticmethod
+    def forward(ctx, pred, noise, latents, weight):
+        B = pred.shape[0]
+        p = check(pred.contiguous(), BF16, "pred")
+        nz = check(noise.contiguous(), BF16, "noise")
+        lat = check(latents.contiguous(), BF16, "latents")
+        w = check(weight.float().reshape(B).contiguous(), torch.float32, "weight", align=4)
+        partials = torch.empty(_lib.lib().tt_flow_loss_blocks(), dtype=torch.float32, device=p.device)
+        loss = torch.empty((), dtype=torch.float32, device=p.device)
+        dpred = torch.empty_like(p) if ctx.needs_input_grad[0] else None
+        call("tt_flow_loss", ptr(p), ptr(nz), ptr(lat), ptr(w), ptr(partials), ptr(dpred), ptr(loss), c_long(p.numel() // B),
+             c_int(B), stream())
+        ctx.save_for_backward(dpred)
+        ctx.shape = pred.shape
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        (dpred,) = ctx.saved_tensors
+        if dpred is None:
+            return None, None, None, None
+        return (dpred * g.to(dpred.dtype)).view(ctx.shape), None, None, None
+
+
+def flow_match_loss(pred, noise, latents, weight):
+    return _FlowMatchLoss.apply(pred, noise, latents, weight)
+
+
+# ---------------------------------------------------------------------------------------------
 # optimizer
 # ---------------------------------------------------------------------------------------------
 

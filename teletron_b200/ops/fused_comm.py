@@ -77,15 +77,39 @@ def saves_need_private_copies() -> bool:
 
 
 class UlyssesWorkspace:
-    """Symmetric buffers of one context-parallel group for a fixed (heads, local sequence, text length)."""
+    """Symmetric buffers of one context-parallel group.  The slab is sized once (for the largest sequence it has to hold)
+    and :meth:`configure` lays the buffers out for the current ``(local sequence, text length)``: clips of different
+    lengths reuse one slab and one set of IPC mappings instead of allocating a heap per shape."""
 
-    def __init__(self, group, heads: int, s_local: int, text_len: int, device=None, heap: Optional[SymmetricHeap] = None):
+    NAMES = ("q", "k", "v", "o", "dq", "dk", "dv", "do")
+
+    @staticmethod
+    def bytes_needed(heads: int, cp: int, s_local: int, text_len: int) -> int:
+        n_qkv = (heads // cp) * (cp * s_local + text_len) * 128 * 2
+        n_g = (text_len + s_local) * heads * 128 * 2
+        return 8 * (n_qkv + 1024) + n_g + 1024
+
+    def __init__(self, group, heads: int, s_local: int, text_len: int, device=None, heap: Optional[SymmetricHeap] = None,
+                 capacity_bytes: Optional[int] = None):
         self.group = group
         self.cp = 1 if group is None else dist.get_world_size(group)
         self.rank = 0 if group is None else dist.get_rank(group)
         if heads % self.cp:
             raise ValueError(f"{heads} heads cannot be split over {self.cp} context-parallel ranks")
         self.heads, self.h_loc = heads, heads // self.cp
+        need = self.bytes_needed(heads, self.cp, s_local, text_len)
+        self.capacity = max(need, capacity_bytes or 0)
+        self.heap = heap or SymmetricHeap(group, self.capacity, device)
+        self.configure(s_local, text_len)
+
+    def fits(self, s_local: int, text_len: int) -> bool:
+        return self.bytes_needed(self.heads, self.cp, s_local, text_len) <= self.capacity
+
+    def configure(self, s_local: int, text_len: int) -> None:
+        """Lay the buffers out for these sequence lengths (same call on every rank: the offsets stay symmetric).  The first
+        fused op that follows starts with a barrier, so no peer still reads the previous layout when it is overwritten."""
+        if not self.fits(s_local, text_len):
+            raise MemoryError("sequence does not fit the workspace it was sized for")
         self.s, self.T = s_local, text_len
         self.S = self.cp * s_local
         self.S_tot = self.S + text_len
@@ -95,11 +119,9 @@ class UlyssesWorkspace:
         self.text_off = 0
         self.video_off = text_len
         n_qkv = self.h_loc * self.S_tot * 128 * 2                  # bytes of one of q / k / v (batch 1)
-        n_g = (text_len + s_local) * heads * 128 * 2               # gathered attention output: my tokens, all heads
-        total = 8 * (n_qkv + 1024) + n_g + 1024
-        self.heap = heap or SymmetricHeap(group, total, device)
-        names = ("q", "k", "v", "o", "dq", "dk", "dv", "do")
-        self.off = {n: self.heap.alloc(n_qkv) for n in names}
+        n_g = (text_len + s_local) * self.heads * 128 * 2          # gathered attention output: my tokens, all heads
+        self.heap.reset()
+        self.off = {n: self.heap.alloc(n_qkv) for n in self.NAMES}
         self.off["g"] = self.heap.alloc(n_g)
 
     def head_major(self, name: str, rank: Optional[int] = None) -> torch.Tensor:
@@ -421,23 +443,34 @@ def fused_attention_outproj(ws: UlyssesWorkspace, q, k, v, w, b, wt, bt, extra=N
 # ---------------------------------------------------------------------------------------------
 
 class TPWorkspace:
-    """Symmetric staging for sequence-sharded tensor parallelism: a gather source and a reduce-scatter landing zone."""
+    """Symmetric staging for sequence-sharded tensor parallelism: a gather source and a reduce-scatter landing zone, sized
+    for ``rows_local`` rows (or more, ``capacity_rows``) and laid out per call of :meth:`configure`."""
 
-    def __init__(self, group, rows_local: int, k_max: int, n_max: int, device=None):
+    def __init__(self, group, rows_local: int, k_max: int, n_max: int, device=None, capacity_rows: Optional[int] = None):
         self.group = group
         self.tp = 1 if group is None else dist.get_world_size(group)
         self.rank = 0 if group is None else dist.get_rank(group)
-        self.rows = rows_local
-        a_bytes = rows_local * k_max * 2
-        s_bytes = self.tp * rows_local * n_max * 2
-        self.heap = SymmetricHeap(group, a_bytes + s_bytes + 4096, device)
-        self.off_a = self.heap.alloc(a_bytes)
-        self.off_s = self.heap.alloc(s_bytes)
         self.k_max, self.n_max = k_max, n_max
+        self.capacity_rows = max(rows_local, capacity_rows or 0)
+        a_bytes = self.capacity_rows * k_max * 2
+        s_bytes = self.tp * self.capacity_rows * n_max * 2
+        self.heap = SymmetricHeap(group, a_bytes + s_bytes + 4096, device)
         dev = self.heap.device
-        self.stage = torch.empty(self.tp * rows_local * k_max, dtype=BF16, device=dev)
-        self.flags = torch.zeros(self.tp * ((rows_local + 127) // 128), dtype=torch.int32, device=dev)
+        self.stage = torch.empty(self.tp * self.capacity_rows * k_max, dtype=BF16, device=dev)
+        self.flags = torch.zeros(self.tp * ((self.capacity_rows + 127) // 128), dtype=torch.int32, device=dev)
         self.epoch = 0
+        self.configure(rows_local)
+
+    def fits(self, rows_local: int) -> bool:
+        return rows_local <= self.capacity_rows
+
+    def configure(self, rows_local: int) -> None:
+        if not self.fits(rows_local):
+            raise MemoryError("row count does not fit the workspace it was sized for")
+        self.rows = rows_local
+        self.heap.reset()
+        self.off_a = self.heap.alloc(rows_local * self.k_max * 2)
+        self.off_s = self.heap.alloc(self.tp * rows_local * self.n_max * 2)
 
 
 def fused_all_gather_linear(ws: TPWorkspace, x_local: torch.Tensor, w: torch.Tensor, bias=None, staged: bool = True) -> torch.Tensor:

@@ -153,6 +153,12 @@ def joint_qkv_projection(x, weight, bias, qw, kw, cos, sin, x2, weight2, bias2, 
     return torch.cat([q, q2], dim=2), torch.cat([k, k2], dim=2), torch.cat([v, v2], dim=2)
 
 
+def noise_mix(latents: torch.Tensor, noise: torch.Tensor, sigma: torch.Tensor) -> torch.Tensor:
+    """``(1 - sigma[b]) * latents + sigma[b] * noise`` in the dtype of ``latents`` (``pipeline.py:118-129``)."""
+    sig = sigma.view(-1, *([1] * (latents.dim() - 1))).to(latents.dtype)
+    return (1.0 - sig) * latents + sig * noise
+
+
 def flow_match_loss(pred: torch.Tensor, noise: torch.Tensor, latents: torch.Tensor,
                     weight: torch.Tensor) -> torch.Tensor:
     """Mean of ``weight * (pred - (noise - latents))^2`` in fp32 (``pipeline.py:215-224``)."""

@@ -28,6 +28,9 @@ def status_tensors(device: Optional[torch.device] = None) -> List[torch.Tensor]:
     return out
 
 
+LAST_CHECK_HOST_TIME = 0.0      # host clock just before the last check blocked on the device (used by the step breakdown)
+
+
 def check_all(group=None, device: Optional[torch.device] = None, what: str = "training step") -> None:
     """Raise :class:`teletron_b200.ops._lib.CommTimeoutError` on every rank of ``group`` if a bounded device-side wait ran
     out on any of them since the last check.  Costs one small all-reduce and one device -> host read."""
@@ -43,6 +46,9 @@ def check_all(group=None, device: Optional[torch.device] = None, what: str = "tr
         on_gpu = torch.cuda.is_available() and dist.get_backend(group) == "nccl"
         code = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()) if on_gpu else "cpu")
     local = code.clone()
+    global LAST_CHECK_HOST_TIME
+    import time
+    LAST_CHECK_HOST_TIME = time.perf_counter()
     if multi:
         dist.all_reduce(code, op=dist.ReduceOp.MAX, group=group)
     worst = int(code.item())

@@ -72,7 +72,7 @@ def test_rank_lists_follow_tp_cp_dp_order():
     assert L["dp"] == [[0, 4], [1, 5], [2, 6], [3, 7]]
     assert L["dp_cp"] == [[0, 2, 4, 6], [1, 3, 5, 7]]
     assert L["tp_cp"] == [[0, 1, 2, 3], [4, 5, 6, 7]]
-    assert rank_coords(6, 2, 2) == {"tp": 0, "cp": 1, "dp": 1}
+    assert rank_coords(6, 2, 2) == {"tp": 0, "cp": 1, "dp": 1, "pp": 0}
     pairs = build_comm_pairs(6, 2, 2, 3)            # 6 DiT ranks (tp2 cp3 -> dp1) + 2 encoder ranks
     # more encoder ranks than DiT groups: both feed the one consumer in turn (the reference would leave rank 7 idle)
     assert [(p.producer, p.consumer, p.lane, p.lanes) for p in pairs] == [(6, 0, 0, 2), (7, 0, 1, 2)]

@@ -261,6 +261,45 @@ def test_fused_ulysses_several_layers_without_per_block_recompute():
     """, timeout=900)
 
 
+def test_fused_workspace_is_reused_across_clip_lengths():
+    """Clips of different lengths through one model: the collective workspace is re-laid-out in place for a shorter clip and
+    replaced (collectively) by a larger one for a longer clip; the loss of every clip equals the NCCL path's."""
+    _run_ranks("""
+        from teletron_b200.models.hunyuanvideo import FlowConfig, HunyuanPipeline, hunyuan_13b
+        from teletron_b200.models.hunyuanvideo import blocks
+        from teletron_b200.parallel import state as ps
+        ps.initialize_model_parallel(1, 2)
+        cfg = hunyuan_13b(in_channels=16, num_layers=1, num_single_layers=1, recompute_granularity="full")
+        gen = torch.Generator().manual_seed(0)
+        def clip(f, h, w):
+            return {"latents": torch.randn(1, 16, f, h, w, generator=gen), "prompt_embeds": torch.randn(1, 40, 4096, generator=gen),
+                    "clip_text_embed": torch.randn(1, 768, generator=gen)}
+        clips = [clip(3, 30, 34), clip(3, 30, 50), clip(2, 30, 34), clip(3, 30, 50)]
+        pipe = HunyuanPipeline(cfg, FlowConfig(model_type="t2v"), device=torch.device("cuda", rank), dtype=torch.bfloat16)
+        losses = {}
+        for fused in (True, False):
+            blocks.set_fused_comm(fused)
+            out = []
+            for i, b in enumerate(clips):
+                for p_ in pipe.parameters():
+                    p_.grad = None
+                pipe.step = i
+                loss = pipe(b)[0]
+                loss.backward()
+                out.append((float(loss.detach()), float(sum(p_.grad.float().abs().sum() for p_ in pipe.transformer.parameters() if p_.grad is not None))))
+            losses[fused] = out
+        kinds = [k for k in blocks._WORKSPACES if k[0] == "ulysses"]
+        assert len(kinds) == 1, kinds                    # one workspace served all four clips
+        for (a, ga), (b, gb) in zip(losses[True], losses[False]):
+            assert abs(a - b) < 2e-2 * abs(b), (losses[True], losses[False])
+            assert abs(ga - gb) < 5e-2 * abs(gb), (ga, gb)
+        from teletron_b200.ops.gemm_tcgen05 import check_status
+        check_status()
+        for ws in blocks._WORKSPACES.values():
+            ws.heap.check()
+    """, timeout=900)
+
+
 def test_sequence_parallel_model_fused_matches_plain_tensor_parallel():
     """One dual + one single block at full width, tp = 2: token-sharded residual stream with the fused all-gather -> GEMM /
     GEMM -> reduce-scatter MLPs against plain tensor parallelism (replicated activations, NCCL all-reduce)."""
