@@ -7,6 +7,7 @@
 // count, per-batch modulation vectors, fp32 arithmetic throughout, (mean, rstd) saved instead of
 // a normalised copy of the activations, and every launch on the caller's stream.
 #include "common.cuh"
+#include "sm100.cuh"
 #include "teletron_b200.h"
 #include "teletron_b200_noalloc.h"
 
@@ -250,6 +251,215 @@ __global__ void __launch_bounds__(MAXT) ln_mod_bwd_kernel(
             p[cols + j] = acc_shift[j];
             if (GATE) p[2 * cols + j] = acc_gate[j];
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward, bulk-copy fed: the same arithmetic as ln_mod_bwd_kernel, but dy and x rows arrive through a shared-memory ring
+// filled by one producer warp with untiled bulk copies (cp.async.bulk, completion on an mbarrier).  What is in flight
+// is then set by the ring (up to ~190 KB per SM) instead of by the registers a thread can spare for pending loads, which
+// kept the register version at a third of the copy bandwidth.  Consumer thread t owns columns [8t, 8t + 8) as before;
+// branch / upstream-gradient rows are fetched with ordinary loads issued before the block reduction.
+// ---------------------------------------------------------------------------------------------
+__device__ int g_norm_status = 0;       // TT_ERR_TIMEOUT when a bounded wait of the ring ran out (read by tt_norm_status)
+
+__device__ __forceinline__ void consumer_sum_batch(float* v, float* red, int parity, int nthreads) {
+    // block_sum_batch for the consumer threads only (named barrier 1: the producer warp never joins it)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = nthreads >> 5;
+    float* r = red + parity * (8 * 32);
+    float a[4], b2[2];
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = (h16 ? v[i + 4] : v[i]) + __shfl_xor_sync(0xffffffffu, h16 ? v[i] : v[i + 4], 16);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) b2[i] = (h8 ? a[i + 2] : a[i]) + __shfl_xor_sync(0xffffffffu, h8 ? a[i] : a[i + 2], 8);
+    float c = (h4 ? b2[1] : b2[0]) + __shfl_xor_sync(0xffffffffu, h4 ? b2[0] : b2[1], 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    if ((lane & 3) == 0) r[(lane >> 2) * 32 + warp] = c;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    float t = 0.f;
+    for (int w = lane >> 3; w < nwarps; w += 4) t += r[(lane & 7) * 32 + w];
+    t += __shfl_xor_sync(0xffffffffu, t, 8);
+    t += __shfl_xor_sync(0xffffffffu, t, 16);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = __shfl_sync(0xffffffffu, t, q);
+}
+
+template <bool GATE, int MAXT>
+__global__ void __launch_bounds__(MAXT + 32) ln_mod_bwd_ring_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ dres_in,
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ branch,
+    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ scale,
+    const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+    __nv_bfloat16* __restrict__ dbranch, float* __restrict__ partials, int cols, long rows_per_batch, int stages) {
+    extern __shared__ uint8_t ring_raw[];
+    __shared__ float red[2 * 8 * 32];
+    __shared__ volatile int abort_flag;
+    using namespace sm100;
+    const uint32_t base = (smem_u32(ring_raw) + 127u) & ~127u;
+    const uint32_t row_bytes = (uint32_t)cols * 2u;
+    const uint32_t stage_bytes = 2u * kRowBatch * row_bytes;              // dy rows then x rows
+    const uint32_t bars = base + (uint32_t)stages * stage_bytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (stages + s); };
+    const int n_cons = blockDim.x - 32;                                     // consumer threads (a multiple of 32)
+    const int t = threadIdx.x;
+    const bool producer = t >= n_cons;
+    const long b = blockIdx.y;
+    if (t == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), n_cons >> 5);
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+    const long first = (long)blockIdx.x * kRowBatch, step = (long)gridDim.x * kRowBatch;
+    if (producer) {
+        if (t == n_cons) {
+            int s = 0;
+            uint32_t phase = 0;
+            for (long r0 = first; r0 < rows_per_batch; r0 += step) {
+                if (!mbar_wait(empty_bar(s), phase ^ 1u, &abort_flag)) break;
+                const int live = (int)min((long)kRowBatch, rows_per_batch - r0);
+                mbar_arrive_expect_tx(full_bar(s), 2u * live * row_bytes);
+                const uint32_t dst = base + (uint32_t)s * stage_bytes;
+                for (int k = 0; k < live; ++k) {
+                    const long row = b * rows_per_batch + r0 + k;
+                    bulk_load_1d(dst + k * row_bytes, dy + row * cols, row_bytes, full_bar(s));
+                    bulk_load_1d(dst + (kRowBatch + k) * row_bytes, x + row * cols, row_bytes, full_bar(s));
+                }
+                if (++s == stages) {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        const int nvec = cols >> 3;
+        const bool active = t < nvec;
+        const float inv_cols = 1.f / (float)cols;
+        float sc1[8], gt[8], acc_scale[8], acc_shift[8], acc_gate[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sc1[j] = 0.f;
+            gt[j] = 0.f;
+            acc_scale[j] = acc_shift[j] = acc_gate[j] = 0.f;
+        }
+        if (active) {
+            unpack8(ld8(scale + b * cols + t * 8), sc1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sc1[j] += 1.f;
+            if (GATE) unpack8(ld8(gate + b * cols + t * 8), gt);
+        }
+        int s = 0, parity = 0;
+        uint32_t phase = 0;
+        for (long r0 = first; r0 < rows_per_batch; r0 += step, parity ^= 1) {
+            const int live = (int)min((long)kRowBatch, rows_per_batch - r0);
+            // rows that do not come through the ring: issue their loads now, they land while the ring data is reduced
+            bf16x8 pup[kRowBatch], pbr[kRowBatch];
+            float mu[kRowBatch], rs[kRowBatch];
+#pragma unroll
+            for (int k = 0; k < kRowBatch; ++k) {
+                const long row = b * rows_per_batch + (k < live ? r0 + k : r0);
+                mu[k] = mean[row];
+                rs[k] = rstd[row];
+                if (active && k < live) {
+                    if (dres_in != nullptr) pup[k] = ld8(dres_in + row * cols + t * 8);
+                    if (GATE) pbr[k] = ld8(branch + row * cols + t * 8);
+                }
+            }
+            if (!mbar_wait(full_bar(s), phase, &abort_flag)) break;
+            // the rows are read from the ring twice (before and after the block reduction) instead of being held in
+            // registers across it; the slot is released after the second read
+            const uint32_t src = base + (uint32_t)s * stage_bytes + (uint32_t)t * 16u;
+            auto ring_row = [&](int which, int k) {
+                uint4 a;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w)
+                             : "r"(src + (uint32_t)(which * kRowBatch + k) * row_bytes) : "memory");
+                return *reinterpret_cast<bf16x8*>(&a);
+            };
+            float sums[2 * kRowBatch];
+#pragma unroll
+            for (int k = 0; k < kRowBatch; ++k) {
+                float s1 = 0.f, s2 = 0.f;
+                if (active && k < live) {
+                    float dyv[8], xv[8];
+                    unpack8(ring_row(0, k), dyv);
+                    unpack8(ring_row(1, k), xv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float xh = (xv[j] - mu[k]) * rs[k];
+                        const float g = dyv[j] * sc1[j];
+                        s1 += g;
+                        s2 += g * xh;
+                        acc_scale[j] += dyv[j] * xh;
+                        acc_shift[j] += dyv[j];
+                    }
+                }
+                sums[2 * k] = s1;
+                sums[2 * k + 1] = s2;
+            }
+            consumer_sum_batch(sums, red, parity, n_cons);
+#pragma unroll
+            for (int k = 0; k < kRowBatch; ++k) {
+                if (active && k < live) {
+                    const long row = b * rows_per_batch + r0 + k;
+                    const float m1 = sums[2 * k] * inv_cols, m2 = sums[2 * k + 1] * inv_cols;
+                    float dyv[8], xv[8], d[8];
+                    unpack8(ring_row(0, k), dyv);
+                    unpack8(ring_row(1, k), xv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float xh = (xv[j] - mu[k]) * rs[k];
+                        d[j] = rs[k] * (dyv[j] * sc1[j] - m1 - xh * m2);
+                    }
+                    if (dres_in != nullptr) {
+                        float up[8];
+                        unpack8(pup[k], up);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) d[j] += up[j];
+                    }
+                    st8(dx + row * cols + t * 8, pack8(d));
+                    if (GATE) {
+                        float br[8], db[8];
+                        unpack8(pbr[k], br);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            acc_gate[j] += d[j] * br[j];
+                            db[j] = d[j] * gt[j];
+                        }
+                        st8(dbranch + row * cols + t * 8, pack8(db));
+                    }
+                }
+            }
+            // every consumer warp has finished with the slot: it can be refilled
+            __syncwarp();
+            if ((t & 31) == 0) mbar_arrive(empty_bar(s));
+            if (++s == stages) {
+                s = 0;
+                phase ^= 1u;
+            }
+        }
+        if (active) {
+            constexpr int K = GATE ? 3 : 2;
+            float* p = partials + ((b * gridDim.x + blockIdx.x) * K) * (long)cols + t * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                p[j] = acc_scale[j];
+                p[cols + j] = acc_shift[j];
+                if (GATE) p[2 * cols + j] = acc_gate[j];
+            }
+        }
+    }
+    __syncthreads();
+    if (abort_flag) {
+        if (t == 0) atomicExch(&g_norm_status, TT_ERR_TIMEOUT);
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);      // let bulk copies in flight land before the ring goes away
     }
 }
 
@@ -584,6 +794,15 @@ inline bool bad_cols(int cols) { return cols <= 0 || (cols & 7) || cols > kMaxCo
 
 extern "C" int tt_norm_partial_blocks(long rows_per_batch, int batch) { return pick_blocks(rows_per_batch, batch); }
 
+// TT_OK, or TT_ERR_TIMEOUT if a bounded wait inside a norm kernel's shared-memory ring ran out since the last call
+// (synchronises the device; the word is cleared).
+extern "C" int tt_norm_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_norm_status, sizeof(int)) != cudaSuccess) return TT_ERR_CUDA;
+    if (v != 0) cudaMemcpyToSymbol(g_norm_status, &zero, sizeof(int));
+    return v;
+}
+
 #define LAUNCH_FWD(VPL)                                                                                         \
     do {                                                                                                        \
         if (has_gate)                                                                                           \
@@ -631,6 +850,38 @@ extern "C" int tt_ln_mod_bwd(const void* dy, const void* dres_in, const void* x,
     const int nblk = pick_blocks(rows_per_batch, batch);
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = (((cols >> 3) + 31) / 32) * 32;
+    int nblk_used = nblk;
+    // Bulk-copy fed ring kernel when at least two stages of four dy + four x rows fit in shared memory (cols <= 6144):
+    // one persistent CTA per SM (fewer partial rows than the register kernel, never more than the caller allocated).
+    const long stage_bytes = 2L * kRowBatch * cols * 2;
+    const int stages = (int)((200 * 1024) / stage_bytes) > 8 ? 8 : (int)((200 * 1024) / stage_bytes);
+    static const bool ring_off = [] { const char* v = getenv("TELETRON_B200_NORM_RING"); return v != nullptr && v[0] == '0'; }();
+    if (stages >= 2 && !ring_off) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int g = sms / batch;
+        if (g < 1) g = 1;
+        if (g > nblk) g = nblk;
+        nblk_used = g;
+        const int smem = (int)(stages * stage_bytes) + 16 * stages + 256;
+        const bool wide = threads > 512;
+        auto kern = has_gate ? (wide ? ln_mod_bwd_ring_kernel<true, 1024> : ln_mod_bwd_ring_kernel<true, 512>)
+                             : (wide ? ln_mod_bwd_ring_kernel<false, 1024> : ln_mod_bwd_ring_kernel<false, 512>);
+        static int configured[4][64] = {{0}};
+        if (dev < 0 || dev >= 64) dev = 0;
+        const int which = (has_gate ? 2 : 0) + (wide ? 1 : 0);
+        if (configured[which][dev] < smem) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return tt_record_cuda(e);
+            configured[which][dev] = smem;
+        }
+        dim3 rgrid(g, batch);
+        kern<<<rgrid, threads + 32, smem, st>>>(
+            (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres_in, (const __nv_bfloat16*)x, (const __nv_bfloat16*)branch,
+            (const __nv_bfloat16*)gate, (const __nv_bfloat16*)scale, mean, rstd, (__nv_bfloat16*)dx, (__nv_bfloat16*)dbranch,
+            partials, cols, rows_per_batch, stages);
+        TT_CHECK_LAUNCH();
+    } else {
     dim3 grid(nblk, batch);
 #define LN_BWD(G_, T_)                                                                                          \
     ln_mod_bwd_kernel<G_, T_><<<grid, threads, 0, st>>>(                                                        \
@@ -645,10 +896,11 @@ extern "C" int tt_ln_mod_bwd(const void* dy, const void* dres_in, const void* x,
         else LN_BWD(false, 1024);
     }
     TT_CHECK_LAUNCH();
+    }
     const int K = has_gate ? 3 : 2;
     dim3 fgrid((cols + 255) / 256, K, batch);
     column_finalize_kernel<<<fgrid, 256, 0, st>>>(partials, (__nv_bfloat16*)dscale, (__nv_bfloat16*)dshift,
-                                                  (__nv_bfloat16*)dgate, K, nblk, cols);
+                                                  (__nv_bfloat16*)dgate, K, nblk_used, cols);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }

@@ -21,6 +21,7 @@ int tt_version(void);
 
 /* ---- LayerNorm + AdaLN modulation (optionally fused with the gated residual update) ---- */
 int tt_norm_partial_blocks(long rows_per_batch, int batch);
+int tt_norm_status(void);      /* TT_ERR_TIMEOUT once if a bounded wait inside a norm kernel ran out; synchronises */
 int tt_ln_mod_fwd(const void* x, const void* branch, const void* gate, const void* scale, const void* shift,
                   void* new_res, void* y, float* mean, float* rstd, long rows, int cols, long rows_per_batch,
                   float eps, void* stream);

@@ -45,10 +45,15 @@ def check_all(group=None, device: Optional[torch.device] = None, what: str = "tr
     else:
         on_gpu = torch.cuda.is_available() and dist.get_backend(group) == "nccl"
         code = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()) if on_gpu else "cpu")
-    local = code.clone()
     global LAST_CHECK_HOST_TIME
     import time
     LAST_CHECK_HOST_TIME = time.perf_counter()
+    if code.is_cuda and _lib.available():
+        # the norm kernels' shared-memory rings report through a word inside the library (a 4-byte read that waits for the device)
+        ns = int(_lib.lib().tt_norm_status())
+        if ns:
+            code = torch.maximum(code, torch.full_like(code, ns))
+    local = code.clone()
     if multi:
         dist.all_reduce(code, op=dist.ReduceOp.MAX, group=group)
     worst = int(code.item())

@@ -19,9 +19,9 @@ def _pipeline(in_channels: int, dev):
     cfg = tiny_config(in_channels=in_channels, hidden_size=256, num_attention_heads=2, attention_head_dim=128,
                       rope_axes_dim=(16, 56, 56), num_layers=1, num_single_layers=1)
     tr = HunyuanVideoTransformer3DModel(cfg, tp=1, device=dev, dtype=torch.bfloat16).eval()
-    vae = AutoencoderKLHunyuanVideo(block_out_channels=(32, 32, 32, 32)).to(dev).eval()
-    llama = LlamaTextEncoder(max_length=24, dtype=torch.float32, config=llama_config(2, 64, 4, 2, 128, 1000)).to(dev)
-    clip = ClipTextEncoder(max_length=16, dtype=torch.float32, config=clip_text_config(2, 32, 4, 500, 16)).to(dev)
+    vae = AutoencoderKLHunyuanVideo(block_out_channels=(32, 32, 32, 32)).to(dev, torch.bfloat16).eval()
+    llama = LlamaTextEncoder(max_length=24, device=dev, dtype=torch.float32, config=llama_config(2, 64, 4, 2, 128, 1000))
+    clip = ClipTextEncoder(max_length=16, device=dev, dtype=torch.float32, config=clip_text_config(2, 32, 4, 500, 16))
     return HunyuanVideoPipeline(tr, vae, llama, clip)
 
 
