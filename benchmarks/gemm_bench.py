@@ -71,11 +71,19 @@ def main():
             else:
                 torch.matmul(As[i].t(), Bs[i], out=out)
         t_lib = timeit(lib, a.iters, rotate)
+        # the CTA-pair kernel (cluster of 2) and the single-CTA kernel, each forced in turn; the dispatcher's own choice
+        # for this shape is whichever the library would pick (pairs when there is a tile per pair of SMs)
+        keep = G.PAIR_KERNEL
+        G.PAIR_KERNEL = False
+        t_single = timeit(ours, a.iters, rotate)
+        G.PAIR_KERNEL = True
+        t_pair = timeit(ours, a.iters, rotate) if G.use_pair_kernel(M, N) else float("nan")
+        G.PAIR_KERNEL = keep
         t_ours = timeit(ours, a.iters, rotate)
         G.check_status()
         fl = 2.0 * M * N * K / 1e12
         rows.append((name, layout, M, N, K, t_ours, fl / (t_ours / 1e3), t_lib, fl / (t_lib / 1e3)))
-        print(f"{name:22s} {layout} M={M:6d} N={N:6d} K={K:6d} | tcgen05 {t_ours:7.3f} ms {fl / (t_ours / 1e3):7.1f} TF "
+        print(f"{name:22s} {layout} M={M:6d} N={N:6d} K={K:6d} | 1-CTA {t_single:7.3f} ms  CTA pair {t_pair:7.3f} ms | tcgen05 {t_ours:7.3f} ms {fl / (t_ours / 1e3):7.1f} TF "
               f"({fl / (t_ours / 1e3) / pk:.2f} of measured peak) | cuBLAS {t_lib:7.3f} ms {fl / (t_lib / 1e3):7.1f} TF "
               f"| ratio {t_lib / t_ours:.2f}", flush=True)
         del As, Bs

@@ -79,6 +79,10 @@ int tt_rs_adamw_ag(void* const* grad_ptrs, int n_g, void* const* param_ptrs, int
 int tt_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
 
+/* the same product on CTA pairs (thread-block cluster of 2, tcgen05.mma.cta_group::2, 256 x 256 tiles; gemm2_tcgen05.cu) */
+int tt_gemm2_bf16(const void* a, const void* b, void* c, const void* bias, void* aux, int M, int N, int K, long lda,
+                  long ldb, long ldc, int a_mn, int b_mn, int epi, int* status, void* stream);
+
 /* pushed tiles (tt_gemm_comm_bf16 store modes 1 / 2): 1 = staged stores of whole 256-byte rows (default), 0 = 16 bytes per thread */
 void tt_set_coalesced_peer_stores(int on);
 

@@ -12,6 +12,7 @@ into :class:`teletron_b200.ops._lib.CommTimeoutError` (the CUDA context stays us
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -21,6 +22,15 @@ from ._lib import c_int, c_long, call, ptr, stream
 
 BF16 = torch.bfloat16
 _LAYOUTS = {"nt": (0, 0), "nn": (0, 1), "tn": (1, 1)}
+# CTA-pair kernel (thread-block cluster of 2, 256 x 256 tiles) for products with at least one tile per pair of SMs;
+# TELETRON_B200_GEMM_2CTA=0 keeps everything on the single-CTA kernel
+PAIR_KERNEL = os.environ.get("TELETRON_B200_GEMM_2CTA", "1") != "0"
+PAIR_MIN_TILES = 74
+COUNTERS = {"pair": 0, "single": 0}
+
+
+def use_pair_kernel(M: int, N: int) -> bool:
+    return PAIR_KERNEL and ((M + 255) // 256) * ((N + 255) // 256) >= PAIR_MIN_TILES
 _STATUS: Dict[torch.device, torch.Tensor] = {}
 
 
@@ -80,7 +90,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, layout: str, bias: Optional[torch.Ten
             raise _lib.NativeError("epilogue 3/4 needs a contiguous [M, N] pre-activation tensor")
     if bias is not None:
         bias = _lib.check(bias.contiguous(), BF16, "bias")
-    call("tt_gemm_bf16", ptr(a), ptr(b), ptr(c), ptr(bias), ptr(aux), c_int(M), c_int(N), c_int(K), c_long(a.stride(0)),
+    pair = use_pair_kernel(M, N)
+    COUNTERS["pair" if pair else "single"] += 1
+    call("tt_gemm2_bf16" if pair else "tt_gemm_bf16", ptr(a), ptr(b), ptr(c), ptr(bias), ptr(aux), c_int(M), c_int(N), c_int(K), c_long(a.stride(0)),
          c_long(b.stride(0)), c_long(c.stride(0)), c_int(a_mn), c_int(b_mn), c_int(epi), ptr(status_tensor(a.device)),
          stream())
     return (c, aux) if epi in (1, 2) else c
