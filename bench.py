@@ -165,7 +165,7 @@ _FAMILIES = (("attention forward", ("tt_attn_fwd",)), ("attention backward", ("t
              ("QKV GEMM + norm + RoPE + seq->head exchange (F1)", ("tt_qkv_gemm_fused",)),
              ("QKV backward: head->seq gather + RoPE^T + norm backward (F1b)", ("tt_qkv_post_bwd",)),
              ("GEMMs with a fused collective (F2b push, F3)", ("tt_gemm_comm", "tt_gemm_ag")),
-             ("plain GEMMs", ("tt_gemm_bf16",)), ("QKV post-processing (unfused path)", ("tt_qkv_post_fwd",)),
+             ("plain GEMMs", ("tt_gemm_bf16", "tt_gemm2_bf16")), ("QKV post-processing (unfused path)", ("tt_qkv_post_fwd",)),
              ("device barriers (includes waiting for the slowest peer)", ("tt_comm_barrier",)),
              ("norm / modulation / gate / GELU", ("tt_ln_mod", "tt_gate_residual", "tt_rmsnorm", "tt_gelu")),
              ("gradient reduce-scatter + parameter all-gather (own kernels)", ("tt_reduce_scatter", "tt_all_gather_push", "tt_rs_adamw")),

@@ -71,6 +71,16 @@ def main():
             o.backward(d)
         t = timeit(ours, a.iters)
         print(f"tcgen05 fwd+bwd  : {t:8.3f} ms  {3.5 * fl / (t / 1e3):7.1f} TFLOP/s")
+        # the backward alone, in both variants: one pass with dQ reduced in fp32 against the deterministic two-kernel split
+        from teletron_b200.ops import attn_bwd_tcgen05 as AB
+        out, lse, *_ = A.forward(q, k, v, None, None)
+        for name, fused in (("one pass", True), ("two kernels", False)) * 2:
+            was = AB.set_fused(fused)
+            t = timeit(lambda: AB.backward(d, q, k, v, out, lse, 128 ** -0.5, S), a.iters)
+            AB.set_fused(was)
+            check_status()
+            print(f"tcgen05 bwd {name:12s}: {t:8.3f} ms  {2.5 * fl / (t / 1e3):7.1f} useful TFLOP/s "
+                  f"({2.5 * fl / (t / 1e3) / pk:.2f} of measured peak)")
         for name, be in (("sdpa cudnn", SDPBackend.CUDNN_ATTENTION), ("sdpa flash", SDPBackend.FLASH_ATTENTION)):
             try:
                 with sdpa_kernel([be]):

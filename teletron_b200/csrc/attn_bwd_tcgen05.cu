@@ -64,6 +64,8 @@ struct BwdParams {
     int* status;
     const __nv_bfloat16* q_raw;     // q [BH, S, 128] and dout [B, S, H * 128] as plain pointers: the variant that keeps the
     const __nv_bfloat16* do_raw;    // stationary operands in tensor memory loads them with ordinary loads
+    float* dq_acc;                  // one-pass variant: fp32 [B*H, s_pad, 128] accumulator for dQ (zeroed by the launcher)
+    int s_pad;                      // rows per head in dq_acc: S rounded up to a multiple of 128
 #ifdef TT_ATTN_STAMPS
     long long* stamps;              // scratch builds only: clock64() of CTA (0, 0)'s pipeline events, [chunk][10]
 #endif
@@ -461,6 +463,385 @@ done:
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// One-pass variant: the key-stationary kernel also forms this chunk's dQ contribution, so S and dP are computed once
+// (five products per [128 x 128] tile pair instead of seven).  dS is written twice by the softmax warps: as bf16 pairs
+// into tensor memory (the A operand of dK += dS^T Q, as above) and into a shared-memory tile laid out [key][query]
+// with 128-byte swizzle, which the tensor core reads MN-major as the A operand of dQ(c) = dS(c) K.  That product lands
+// in T2 once dK(c) / dV(c) have consumed the bf16 P / dS there (the tensor core executes in issue order); the softmax
+// warps read it back and add it to an fp32 [B*H, s_pad, 128] accumulator in global memory with vector reductions
+// (every key tile of a head adds into the same rows: the order of those additions is not fixed, so dQ is reproducible
+// only to fp32 rounding).  A last elementwise kernel scales and rounds the accumulator to bf16.
+//
+//   tensor core:  dP(c) S(c+1) ............ | dK(c) dV(c) dQ(c) | dP(c+1) S(c+2) ...
+//   softmax:      readout(c-1) | dS(c) .... | P(c+1) .......... | readout(c) | dS(c+1) ...
+//
+// Shared memory: K, V resident; two slots each for the streamed Q and dO; one dS tile (same 225 KB as above).
+constexpr int kFRing = 2;
+constexpr int kFSmemBytes = (2 + 2 * kFRing + 1) * kTile + 256 + 1024;
+
+// TMA reduction shared -> global: adds the [32 x 32] fp32 box at `smem_src` (128-byte swizzle) into the tensor at (x, y)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, uint32_t smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     (uint64_t)tmap),
+                 "r"(smem_src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                      const __grid_constant__ CUtensorMap tmDQ, const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ volatile int abort_flag;
+    __shared__ uint32_t tmem_base_slot;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sA1 = base;                       // K tile
+    const uint32_t sA2 = base + kTile;               // V tile
+    const uint32_t sRing1 = base + 2 * kTile;        // Q chunks
+    const uint32_t sRing2 = sRing1 + kFRing * kTile; // dO chunks
+    const uint32_t sDS = sRing2 + kFRing * kTile;    // dS of the current chunk, [key][query] bf16
+    const uint32_t bars = sDS + kTile;
+    const uint32_t a_full = bars;
+    auto b1_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto b1_empty = [&](int s) { return bars + 8u * (1 + kFRing + s); };
+    auto b2_full = [&](int s) { return bars + 8u * (1 + 2 * kFRing + s); };
+    auto b2_empty = [&](int s) { return bars + 8u * (1 + 3 * kFRing + s); };
+    const uint32_t s_full = bars + 8u * (1 + 4 * kFRing);
+    const uint32_t dp_full = s_full + 8u;
+    const uint32_t p_ready = s_full + 16u;
+    const uint32_t ds_ready = s_full + 24u;
+    const uint32_t dq_full = s_full + 32u;           // T2 holds dQ(c)
+    const uint32_t dq_read = s_full + 40u;           // every softmax warp has read dQ(c) out of T2
+    const uint32_t acc_final = s_full + 48u;
+    const uint32_t stage_done = s_full + 56u;        // the dQ(c) read-out staged in the dS tile has been read by the TMA unit
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bh = blockIdx.y;
+    const int b = bh / p.H, head = bh - b * p.H;
+    const int r0 = blockIdx.x * BS;                  // first key of this CTA
+    const int n_chunks = (p.S + BC - 1) / BC;        // query chunks
+    // Key tile x starts at query chunk x and wraps around: at any moment the CTAs of a head work on different chunks, so
+    // their dQ reductions land on different lines of the accumulator instead of queueing up on the same 64 KB.
+    const int c0 = (int)blockIdx.x % n_chunks;
+    auto chunk_of = [&](int c) { const int e = c + c0; return e >= n_chunks ? e - n_chunks : e; };
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(a_full, 1);
+        for (int s = 0; s < kFRing; ++s) {
+            mbar_init(b1_full(s), 1);
+            mbar_init(b1_empty(s), 1);
+            mbar_init(b2_full(s), 1);
+            mbar_init(b2_empty(s), 1 + 2 * kGroups);     // dV(c) done + the eight warps that stage dQ(c) in this slot
+        }
+        mbar_init(s_full, 1);
+        mbar_init(dp_full, 1);
+        mbar_init(p_ready, 4 * kGroups);
+        mbar_init(ds_ready, 4 * kGroups);
+        mbar_init(dq_full, 1);
+        mbar_init(dq_read, 4 * kGroups);
+        mbar_init(acc_final, 1);
+        mbar_init(stage_done, 2 * kGroups);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_slot;
+    constexpr uint32_t kT1 = 0, kT2 = 128, kAccV = 256, kAccK = 384;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(a_full, 2 * kTile);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                tma_load_3d(sA1 + h * kSlab, &tmK, a_full, h * 64, r0, bh);
+                tma_load_3d(sA2 + h * kSlab, &tmV, a_full, h * 64, r0, bh);
+            }
+            for (int c = 0; c < n_chunks; ++c) {
+                const int s = c % kFRing;
+                const uint32_t wpar = ((uint32_t)(c / kFRing) & 1u) ^ 1u;
+                if (!mbar_wait(b1_empty(s), wpar, &abort_flag)) goto done;
+                mbar_arrive_expect_tx(b1_full(s), kTile);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) tma_load_3d(sRing1 + s * kTile + h * kSlab, &tmQ, b1_full(s), h * 64, chunk_of(c) * BC, bh);
+                if (!mbar_wait(b2_empty(s), wpar, &abort_flag)) goto done;
+                mbar_arrive_expect_tx(b2_full(s), kTile);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    tma_load_4d(sRing2 + s * kTile + h * kSlab, &tmDO, b2_full(s), h * 64, head, chunk_of(c) * BC, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_t = idesc_bf16(BS, BC, false, false);   // T = A B^T, both K-major
+            constexpr uint32_t idesc_a = idesc_bf16(BS, D, false, true);     // acc += (tensor-memory A) B, B MN-major
+            constexpr uint32_t idesc_q = idesc_bf16(BC, D, true, true);      // dQ = dS K: both operands MN-major
+            auto issue_t = [&](uint32_t t_col, uint32_t sa, uint32_t sb) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t o = (kk >> 2) * kSlab + (kk & 3) * 32;
+                    umma_bf16_ss(tmem + t_col, smem_desc_sw128(sa + o, 16, 1024), smem_desc_sw128(sb + o, 16, 1024), idesc_t,
+                                 kk ? 1u : 0u);
+                }
+            };
+            auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t sb, bool first) {
+#pragma unroll
+                for (int kk = 0; kk < BC / 16; ++kk)
+                    umma_bf16_ts(tmem + acc_col, tmem + a_col + (kk >> 1) * kCols + (kk & 1) * 8,
+                                 smem_desc_sw128(sb + kk * 2048, kSlab, 1024), idesc_a, (first && kk == 0) ? 0u : 1u);
+            };
+            if (!mbar_wait(a_full, 0, &abort_flag)) goto done;
+            if (!mbar_wait(b1_full(0), 0, &abort_flag)) goto done;
+            tc_fence_after();
+            issue_t(kT1, sA1, sRing1);
+            umma_commit(s_full);
+            if (!mbar_wait(b2_full(0), 0, &abort_flag)) goto done;
+            tc_fence_after();
+            issue_t(kT2, sA2, sRing2);
+            umma_commit(dp_full);
+            for (int c = 0; c < n_chunks; ++c) {
+                const uint32_t par = (uint32_t)c & 1u;
+                const bool more = c + 1 < n_chunks;
+                const int slot = c % kFRing, nslot = (c + 1) % kFRing;
+                const uint32_t npar = (uint32_t)((c + 1) / kFRing) & 1u;
+                TT_STAMP(0);
+                if (!mbar_wait(p_ready, par, &abort_flag)) goto done;              // S(c) has been read: T1 is free
+                TT_STAMP(1);
+                tc_fence_after();
+                if (more) {
+                    if (!mbar_wait(b1_full(nslot), npar, &abort_flag)) goto done;
+                    tc_fence_after();
+                    issue_t(kT1, sA1, sRing1 + nslot * kTile);                     // S(c+1)
+                    umma_commit(s_full);
+                }
+                if (!mbar_wait(ds_ready, par, &abort_flag)) goto done;             // P, dS in T2; dS in shared memory
+                TT_STAMP(2);
+                tc_fence_after();
+                issue_acc(kAccK, kT2 + 16, sRing1 + slot * kTile, c == 0);          // dK += dS^T Q
+                umma_commit(b1_empty(slot));
+                issue_acc(kAccV, kT2, sRing2 + slot * kTile, c == 0);               // dV += P^T dO
+                umma_commit(b2_empty(slot));
+#pragma unroll
+                for (int kk = 0; kk < BS / 16; ++kk)                                // dQ(c) = dS K over the 128 keys, into T2
+                    umma_bf16_ss(tmem + kT2, smem_desc_sw128(sDS + kk * 2048, kSlab, 1024),
+                                 smem_desc_sw128(sA1 + kk * 2048, kSlab, 1024), idesc_q, kk ? 1u : 0u);
+                umma_commit(dq_full);
+                TT_STAMP(3);
+                if (more) {
+                    if (!mbar_wait(dq_read, par, &abort_flag)) goto done;          // dQ(c) is in registers: T2 is free
+                    TT_STAMP(4);
+                    if (!mbar_wait(b2_full(nslot), npar, &abort_flag)) goto done;
+                    tc_fence_after();
+                    issue_t(kT2, sA2, sRing2 + nslot * kTile);                     // dP(c+1)
+                    umma_commit(dp_full);
+                }
+            }
+            umma_commit(acc_final);
+        }
+    } else {
+        // ------------------------------------------------------------ softmax / dS / dQ read-out
+        const int part = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int srow = quad * 32 + lane;                 // key row within the tile; also the query row of a dQ read-out
+        const int row = r0 + srow;
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        const float c_log2 = p.scale * kLog2e;
+        const bool row_live = row < p.kv_len && !(row >= p.mask_lo && row < p.mask_hi);
+        const uint32_t t1 = tmem + lane_sel + kT1 + part * kCols, t2 = tmem + lane_sel + kT2 + part * kCols;
+        // this thread's 64 bytes of the dS tile: row srow of slab (part >> 1), 16-byte chunks 4 (part & 1) + 0..3, swizzled
+        const uint32_t ds_row = sDS + (uint32_t)(part >> 1) * kSlab + (uint32_t)srow * 128u;
+        const uint32_t ds_chunk0 = (uint32_t)(part & 1) * 4u, ds_xor = (uint32_t)srow & 7u;
+        uint32_t pk[16];
+
+        auto p_pass = [&](int c) -> bool {
+            const int col0 = chunk_of(c) * BC + part * kCols;
+            const bool cols_ok = col0 < p.pitch;
+            const float4* lse4 = reinterpret_cast<const float4*>(p.lse + (long)bh * p.pitch + col0);
+            if (!mbar_wait(s_full, (uint32_t)c & 1u, &abort_flag)) return false;
+            tc_fence_after();
+            uint32_t a[32];
+            tmem_ld_32x32(t1, a);
+            float4 lq[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) lq[i] = cols_ok ? __ldg(lse4 + i) : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float4 lv = lq[i >> 1];
+                const float2 l2 = (i & 1) ? make_float2(lv.z * kLog2e, lv.w * kLog2e) : make_float2(lv.x * kLog2e, lv.y * kLog2e);
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1])),
+                                            make_float2(c_log2, c_log2), make_float2(-l2.x, -l2.y));
+                float2 pr = make_float2(exp2f(x.x), exp2f(x.y));
+                if (!row_live) pr = make_float2(0.f, 0.f);
+                const __nv_bfloat162 pb = __floats2bfloat162_rn(pr.x, pr.y);
+                pk[i] = *reinterpret_cast<const uint32_t*>(&pb);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+            return true;
+        };
+
+        if (!p_pass(0)) goto done;
+        for (int c = 0; c < n_chunks; ++c) {
+            const uint32_t par = (uint32_t)c & 1u;
+            const int col0 = chunk_of(c) * BC + part * kCols;
+            const bool cols_ok = col0 < p.pitch;
+            const float4* del4 = reinterpret_cast<const float4*>(p.delta + (long)bh * p.pitch + col0);
+            // ---- dS(c) from dP(c) and the P kept in registers
+            if (!mbar_wait(dp_full, par, &abort_flag)) goto done;
+            if (threadIdx.x == 64) TT_STAMP(5);
+            tc_fence_after();
+            uint32_t dk[16];
+            {
+                uint32_t g[32];
+                tmem_ld_32x32(t2, g);
+                float4 dq4[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dq4[i] = cols_ok ? __ldg(del4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 dv = dq4[i >> 1];
+                    const float2 d2 = (i & 1) ? make_float2(dv.z, dv.w) : make_float2(dv.x, dv.y);
+                    const float2 pr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[i]));
+                    const float2 dp = make_float2(__uint_as_float(g[2 * i]) - d2.x, __uint_as_float(g[2 * i + 1]) - d2.y);
+                    const float2 ds = __fmul2_rn(pr, dp);
+                    const __nv_bfloat162 db = __floats2bfloat162_rn(ds.x, ds.y);
+                    dk[i] = *reinterpret_cast<const uint32_t*>(&db);
+                }
+            }
+            tmem_st_32x16(t2, pk);
+            tmem_st_32x16(t2 + 16, dk);
+            // the dS tile doubles as a staging buffer of the previous chunk's dQ read-out: wait until that has left
+            if (c > 0) {
+                if (part < 2 && lane == 0) {
+                    bulk_wait_read();
+                    mbar_arrive(stage_done);
+                }
+                if (!mbar_wait(stage_done, (uint32_t)(c - 1) & 1u, &abort_flag)) goto done;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t addr = ds_row + (((ds_chunk0 + (uint32_t)j) ^ ds_xor) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(dk[4 * j]), "r"(dk[4 * j + 1]),
+                             "r"(dk[4 * j + 2]), "r"(dk[4 * j + 3])
+                             : "memory");
+            }
+            tmem_st_wait();
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ds_ready);
+            if (threadIdx.x == 64) TT_STAMP(6);
+            if (c > 0 && part >= 2 && lane == 0) {         // the other half of dQ(c-1) was staged in that chunk's dO slot
+                bulk_wait_read();
+                mbar_arrive(b2_empty((c - 1) % kFRing));
+            }
+            // ---- P(c+1): runs while the tensor core forms dK(c), dV(c), dQ(c)
+            if (c + 1 < n_chunks && !p_pass(c + 1)) goto done;
+            if (threadIdx.x == 64) TT_STAMP(7);
+            // ---- dQ(c) out of T2 and into the global accumulator
+            if (!mbar_wait(dq_full, par, &abort_flag)) goto done;
+            if (threadIdx.x == 64) TT_STAMP(8);
+            tc_fence_after();
+            uint32_t r[32];
+            tmem_ld_32x32(t2, r);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dq_read);
+            // Staging for the TMA reduction, 4 KB per warp: column groups 0, 1 use the dS tile (idle until the next chunk's
+            // dS is stored), groups 2, 3 this chunk's dO slot (dV(c) has consumed it; the producer refills it only after
+            // these warps have released it).  The reductions drain while the next chunk is computed.
+            {
+                const int g = quad * 2 + (part & 1);
+                const uint32_t region = (part < 2 ? sDS : sRing2 + (uint32_t)(c % kFRing) * kTile) + ((uint32_t)g << 12);
+                const uint32_t mine = region + (uint32_t)lane * 128u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(mine + ((((uint32_t)j) ^ ((uint32_t)lane & 7u)) << 4)),
+                                 "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                                 : "memory");
+                fence_proxy_async();
+                __syncwarp();
+#ifndef TT_FUSED_NO_RED
+                if (lane == 0) {
+                    tma_reduce_add_2d(&tmDQ, region, part * kCols, bh * p.s_pad + chunk_of(c) * BC + quad * 32);
+                    bulk_commit();
+                }
+#endif
+            }
+            if (threadIdx.x == 64) TT_STAMP(9);
+        }
+        if (lane == 0) bulk_wait_all();
+        // ------------------------------------------------------------ epilogue: dV (unscaled), dK (x softmax scale)
+        if (!mbar_wait(acc_final, 0, &abort_flag)) goto done;
+        tc_fence_after();
+        const bool store = row < p.S;
+        const long orow = ((long)bh * p.S + row) * D;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+            __nv_bfloat16* dst = (which == 0 ? p.out1 : p.out2) + orow;
+            const float mul = which == 0 ? 1.f : p.scale;
+            const uint32_t tacc = tmem + lane_sel + kAccV + which * 128;
+            uint32_t r[32];
+            tmem_ld_32x32(tacc + part * 32, r);
+            tmem_ld_wait();
+            if (store) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    float o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[g * 8 + i]) * mul;
+                    tt::st8(dst + part * 32 + g * 8, tt::pack8(o));
+                }
+            }
+        }
+    }
+
+done:
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, TT_ERR_TIMEOUT);
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// dq[bh, s, :] = bf16(scale * acc[bh, s, :]); eight elements per thread
+__global__ void __launch_bounds__(256) dq_finish_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long BH, int S,
+                                                       int s_pad, float scale) {
+    const long n8 = BH * S * (D / 8);
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+        const long rowi = i / (D / 8);
+        const int c8 = (int)(i - rowi * (D / 8));
+        const long bhi = rowi / S, s = rowi - bhi * S;
+        const float4* src = reinterpret_cast<const float4*>(acc + (bhi * s_pad + s) * D + c8 * 8);
+        const float4 x = __ldg(src), y = __ldg(src + 1);
+        float o[8] = {x.x * scale, x.y * scale, x.z * scale, x.w * scale, y.x * scale, y.y * scale, y.z * scale, y.w * scale};
+        tt::st8(dq + rowi * D + c8 * 8, tt::pack8(o));
+    }
+}
+
 }  // namespace
 
 // lse, delta: [B*H, pitch] fp32 with pitch a multiple of 64; lse holds +inf and delta 0 at positions >= S
@@ -515,6 +896,8 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
     p.status = status;
     p.q_raw = (const __nv_bfloat16*)q;
     p.do_raw = (const __nv_bfloat16*)dout;
+    p.dq_acc = nullptr;
+    p.s_pad = 0;
 #ifdef TT_ATTN_STAMPS
     p.stamps = g_attn_stamps;
 #endif
@@ -535,6 +918,83 @@ extern "C" int tt_attn_bwd(const void* q, const void* k, const void* v, const vo
         attn_bwd_kernel<false, true><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
     else
         attn_bwd_kernel<false><<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, p);
+    TT_CHECK_LAUNCH();
+    return TT_OK;
+}
+
+// One-pass backward: delta preprocess, the fused key-stationary kernel (dK, dV written, dQ accumulated in fp32 into
+// `dq_acc`), then the scale-and-round pass into `dq`.  dq_acc: fp32 scratch of B * H * s_pad * 128 elements with
+// s_pad = S rounded up to a multiple of 128; it is zeroed here.
+extern "C" int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                 const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int H,
+                                 int S, int kv_len, int mask_lo, int mask_hi, int pitch, float scale, int* status,
+                                 void* stream) {
+    if (B <= 0 || H <= 0 || S <= 0 || kv_len <= 0 || kv_len > S || status == nullptr || delta == nullptr || dq_acc == nullptr)
+        return TT_ERR_ARG;
+    if (mask_lo < mask_hi && (mask_lo < 0 || (mask_lo == 0 && mask_hi >= kv_len))) return TT_ERR_ARG;
+    if (pitch < S || (pitch & 63) || ((uintptr_t)lse & 15) || ((uintptr_t)delta & 15) || ((uintptr_t)dq_acc & 15)) return TT_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint64_t BH = (uint64_t)B * H;
+    const int s_pad = (S + BC - 1) / BC * BC;
+    CUtensorMap tq_s, tk_s, tv_s, tdo_s;
+    int rc;
+    if ((rc = tt_make_tmap_3d(&tq_s, q, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
+    if ((rc = tt_make_tmap_3d(&tk_s, k, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
+    if ((rc = tt_make_tmap_3d(&tv_s, v, BH, (uint64_t)S, D, D, (uint64_t)S * D, BS, 64)) != TT_OK) return rc;
+    if ((rc = tt_make_tmap_bshd(&tdo_s, dout, (uint64_t)B, (uint64_t)S, (uint64_t)H, BS)) != TT_OK) return rc;
+    static bool configured_dev[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!configured_dev[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmemBytes);
+        if (e != cudaSuccess) return tt_record_cuda(e);
+        configured_dev[dev] = true;
+    }
+    CUtensorMap tdq;      // fp32 [B*H*s_pad, 128], boxes of 32 rows x 32 columns (128 bytes), 128-byte swizzle
+    {
+        tt_encode_tiled_fn enc = tt_get_encode_tiled();
+        if (enc == nullptr) return TT_ERR_CUDA;
+        cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)(BH * (uint64_t)s_pad)};
+        cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(float)};
+        cuuint32_t box[2] = {32, 32};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dq_acc, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return TT_ERR_ARG;
+    }
+    cudaError_t e = cudaMemsetAsync(dq_acc, 0, BH * (uint64_t)s_pad * D * sizeof(float), st);
+    if (e != cudaSuccess) return tt_record_cuda(e);
+    const long nwork = (long)B * S * H;
+    long want = (nwork + 7) / 8;
+    delta_kernel<<<(int)(want < 148L * 16 ? want : 148L * 16), 256, 0, st>>>((const __nv_bfloat16*)dout,
+                                                                            (const __nv_bfloat16*)out, delta, B, S, H, pitch);
+    TT_CHECK_LAUNCH();
+    BwdParams p;
+    p.lse = lse;
+    p.delta = delta;
+    p.S = S;
+    p.kv_len = kv_len;
+    p.mask_lo = mask_lo;
+    p.mask_hi = mask_lo < mask_hi ? mask_hi : mask_lo;
+    p.H = H;
+    p.pitch = pitch;
+    p.scale = scale;
+    p.status = status;
+    p.q_raw = (const __nv_bfloat16*)q;
+    p.do_raw = (const __nv_bfloat16*)dout;
+    p.dq_acc = dq_acc;
+    p.s_pad = s_pad;
+#ifdef TT_ATTN_STAMPS
+    p.stamps = g_attn_stamps;
+#endif
+    p.out1 = (__nv_bfloat16*)dv;
+    p.out2 = (__nv_bfloat16*)dk;
+    attn_bwd_fused_kernel<<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kFSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, tdq, p);
+    TT_CHECK_LAUNCH();
+    const long n8 = (long)BH * S * (D / 8);
+    long blocks = (n8 + 255) / 256;
+    dq_finish_kernel<<<(int)(blocks < 148L * 16 ? blocks : 148L * 16), 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, (long)BH, S, s_pad,
+                                                                                   scale);
     TT_CHECK_LAUNCH();
     return TT_OK;
 }

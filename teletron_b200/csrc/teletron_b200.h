@@ -108,6 +108,10 @@ int tt_attn_fwd_push(const void* q, const void* k, const void* v, void* out, flo
 int tt_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
                 float* delta, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len, int mask_lo, int mask_hi,
                 int pitch, float scale, int* status, void* stream);
+/* one pass over the scores: dQ accumulated in fp32 scratch dq_acc [B*H, roundup(S,128), 128] with vector reductions */
+int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                      float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int H, int S, int kv_len,
+                      int mask_lo, int mask_hi, int pitch, float scale, int* status, void* stream);
 
 /* ---- symmetric heap + in-kernel collectives over IPC-mapped peer memory (comm.cu) ---- */
 int tt_symm_alloc(size_t bytes, void** out);                 /* cudaMalloc + zero */

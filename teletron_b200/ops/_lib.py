@@ -96,7 +96,7 @@ def check(t: torch.Tensor, dtype: torch.dtype, name: str, device: Optional[torch
 
 
 # kernels launched per native call (for the launch counter the benchmark reports)
-KERNELS_PER_CALL = {"tt_ln_mod_bwd": 2, "tt_gate_residual_bwd": 2, "tt_rmsnorm_bwd": 2, "tt_qkv_post_bwd": 2, "tt_attn_bwd": 3}
+KERNELS_PER_CALL = {"tt_ln_mod_bwd": 2, "tt_gate_residual_bwd": 2, "tt_rmsnorm_bwd": 2, "tt_qkv_post_bwd": 2, "tt_attn_bwd": 3, "tt_attn_bwd_fused": 3}
 LAUNCHES = 0
 
 

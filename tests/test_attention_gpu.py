@@ -8,6 +8,17 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["fused", "split"])
+def bwd_variant(request):
+    """Run a backward test on the one-pass kernel (dQ by fp32 reductions) and on the deterministic two-kernel split."""
+    from teletron_b200.ops import attn_bwd_tcgen05 as AB
+    was = AB.set_fused(request.param == "fused")
+    before = dict(AB.COUNTERS)
+    yield request.param
+    assert AB.COUNTERS[request.param] > before[request.param]
+    AB.set_fused(was)
+
+
 def _rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
 
@@ -54,8 +65,8 @@ def test_forward_large_scores_trigger_rescale():
     torch.testing.assert_close(lse[..., :S], rl, rtol=2e-3, atol=5e-3)
 
 
-@pytest.mark.parametrize("S,kv_len", [(640, None), (300, 260), (128, None), (1000, None), (2100, 2000)])
-def test_autograd_matches_reference(S, kv_len):
+@pytest.mark.parametrize("S,kv_len", [(640, None), (300, 260), (128, None), (1000, None), (2100, 2000), (77, None)])
+def test_autograd_matches_reference(S, kv_len, bwd_variant):
     from teletron_b200.ops import attn_tcgen05 as A
     from teletron_b200.ops import reference
     g = torch.Generator(device="cuda").manual_seed(1)
@@ -72,7 +83,7 @@ def test_autograd_matches_reference(S, kv_len):
 
 
 @pytest.mark.parametrize("S,kv_len,mask", [(900, None, (40, 256)), (700, 650, (100, 130)), (640, None, (128, 256)), (400, 390, (3, 5))])
-def test_masked_key_range_forward_and_backward(S, kv_len, mask):
+def test_masked_key_range_forward_and_backward(S, kv_len, mask, bwd_variant):
     """Padded text tokens that sit at the head of the sequence: keys in [lo, hi) are masked on top of the key length,
     including a range that covers a whole 128-key tile."""
     from teletron_b200.ops import attn_tcgen05 as A
@@ -96,9 +107,11 @@ def test_masked_key_range_forward_and_backward(S, kv_len, mask):
     assert float(v.grad[:, :, mask[0]:mask[1]].float().abs().max()) == 0.0
 
 
-def test_forward_and_backward_are_bitwise_reproducible():
-    """No atomics and a fixed accumulation order in both backward kernels: repeated launches on the same inputs give the
-    same bits (also a cheap detector of ordering races between the kernels' warp roles)."""
+def test_forward_and_backward_are_bitwise_reproducible(bwd_variant):
+    """The forward, dK and dV have a fixed accumulation order in both variants; so has dQ in the two-kernel split:
+    repeated launches on the same inputs give the same bits (also a cheap detector of ordering races between the
+    kernels' warp roles).  The one-pass variant adds the key tiles' dQ contributions in fp32 in no fixed order: there
+    dQ repeats to rounding."""
     from teletron_b200.ops import attn_tcgen05 as A
     from teletron_b200.ops.gemm_tcgen05 import check_status
     g = torch.Generator(device="cuda").manual_seed(4)
@@ -114,6 +127,9 @@ def test_forward_and_backward_are_bitwise_reproducible():
         if first is None:
             first = res
         else:
-            for a, b in zip(res, first):
-                assert torch.equal(a, b)
+            for i, (a, b) in enumerate(zip(res, first)):
+                if i == 1 and bwd_variant == "fused":
+                    assert _rel(a, b) < 2e-3
+                else:
+                    assert torch.equal(a, b)
     check_status()
