@@ -490,9 +490,11 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, uint3
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_but_last() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-__global__ void __launch_bounds__(kThreads, 1)
+constexpr int kFThreads = kThreads + 32;     // one more warp: issues the dQ reductions and waits for them
+__global__ void __launch_bounds__(kFThreads, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmDQ, const BwdParams p) {
@@ -519,7 +521,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t dq_full = s_full + 32u;           // T2 holds dQ(c)
     const uint32_t dq_read = s_full + 40u;           // every softmax warp has read dQ(c) out of T2
     const uint32_t acc_final = s_full + 48u;
-    const uint32_t stage_done = s_full + 56u;        // the dQ(c) read-out staged in the dS tile has been read by the TMA unit
+    const uint32_t stage_done = s_full + 56u;        // the dQ(c) half staged in the dS tile has been read by the TMA unit
+    const uint32_t staged_a = s_full + 64u;          // column groups 0, 1 of dQ(c) are in the dS tile
+    const uint32_t staged_b = s_full + 72u;          // column groups 2, 3 of dQ(c) are in chunk c's dO slot
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bh = blockIdx.y;
@@ -538,7 +542,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             mbar_init(b1_full(s), 1);
             mbar_init(b1_empty(s), 1);
             mbar_init(b2_full(s), 1);
-            mbar_init(b2_empty(s), 1 + 2 * kGroups);     // dV(c) done + the eight warps that stage dQ(c) in this slot
+            mbar_init(b2_empty(s), 2);     // dV(c) has read the slot + the dQ half staged in it afterwards has left
         }
         mbar_init(s_full, 1);
         mbar_init(dp_full, 1);
@@ -547,7 +551,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(dq_full, 1);
         mbar_init(dq_read, 4 * kGroups);
         mbar_init(acc_final, 1);
-        mbar_init(stage_done, 2 * kGroups);
+        mbar_init(stage_done, 1);
+        mbar_init(staged_a, 2 * kGroups);
+        mbar_init(staged_b, 2 * kGroups);
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -652,6 +658,38 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
             umma_commit(acc_final);
         }
+    } else if (warp == 2 + 4 * kGroups) {
+        // ------------------------------------------------------------ dQ reductions
+        // dQ(c) is staged by the softmax warps in two halves of eight [32 x 32] fp32 boxes: column groups 0, 1 in the dS
+        // tile (idle until the next chunk's dS is stored), groups 2, 3 in chunk c's dO slot (dV(c) has consumed it; the
+        // producer refills it only after this thread has released it).  The first half is issued first, so it leaves
+        // first; both drain while the next chunk is computed.  A thread of its own waits for the TMA unit, so that no
+        // softmax warp ever does.
+        if (lane == 0) {
+            for (int c = 0; c < n_chunks; ++c) {
+                const uint32_t par = (uint32_t)c & 1u;
+                const int yrow = bh * p.s_pad + chunk_of(c) * BC;
+                if (!mbar_wait(staged_a, par, &abort_flag)) goto done;
+#ifndef TT_FUSED_NO_RED
+#pragma unroll
+                for (int g = 0; g < 8; ++g) tma_reduce_add_2d(&tmDQ, sDS + ((uint32_t)g << 12), (g & 1) * kCols, yrow + (g >> 1) * 32);
+#endif
+                bulk_commit();
+                if (!mbar_wait(staged_b, par, &abort_flag)) goto done;
+#ifndef TT_FUSED_NO_RED
+                const uint32_t slot = sRing2 + (uint32_t)(c % kFRing) * kTile;
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    tma_reduce_add_2d(&tmDQ, slot + ((uint32_t)g << 12), (2 + (g & 1)) * kCols, yrow + (g >> 1) * 32);
+#endif
+                bulk_commit();
+                bulk_wait_read_but_last();
+                mbar_arrive(stage_done);
+                bulk_wait_read();
+                mbar_arrive(b2_empty(c % kFRing));
+            }
+            bulk_wait_all();
+        }
     } else {
         // ------------------------------------------------------------ softmax / dS / dQ read-out
         const int part = (warp - 2) >> 2;
@@ -666,6 +704,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t ds_row = sDS + (uint32_t)(part >> 1) * kSlab + (uint32_t)srow * 128u;
         const uint32_t ds_chunk0 = (uint32_t)(part & 1) * 4u, ds_xor = (uint32_t)srow & 7u;
         uint32_t pk[16];
+        // this warp's 4 KB of the dQ staging: groups 0, 1 in the dS tile, groups 2, 3 in the chunk's dO slot
+        const uint32_t stage_off = ((uint32_t)(quad * 2 + (part & 1)) << 12) + (uint32_t)lane * 128u;
 
         auto p_pass = [&](int c) -> bool {
             const int col0 = chunk_of(c) * BC + part * kCols;
@@ -728,13 +768,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tmem_st_32x16(t2, pk);
             tmem_st_32x16(t2 + 16, dk);
             // the dS tile doubles as a staging buffer of the previous chunk's dQ read-out: wait until that has left
-            if (c > 0) {
-                if (part < 2 && lane == 0) {
-                    bulk_wait_read();
-                    mbar_arrive(stage_done);
-                }
-                if (!mbar_wait(stage_done, (uint32_t)(c - 1) & 1u, &abort_flag)) goto done;
-            }
+            if (c > 0 && !mbar_wait(stage_done, (uint32_t)(c - 1) & 1u, &abort_flag)) goto done;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint32_t addr = ds_row + (((ds_chunk0 + (uint32_t)j) ^ ds_xor) << 4);
@@ -748,10 +782,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_ready);
             if (threadIdx.x == 64) TT_STAMP(6);
-            if (c > 0 && part >= 2 && lane == 0) {         // the other half of dQ(c-1) was staged in that chunk's dO slot
-                bulk_wait_read();
-                mbar_arrive(b2_empty((c - 1) % kFRing));
-            }
             // ---- P(c+1): runs while the tensor core forms dK(c), dV(c), dQ(c)
             if (c + 1 < n_chunks && !p_pass(c + 1)) goto done;
             if (threadIdx.x == 64) TT_STAMP(7);
@@ -765,13 +795,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dq_read);
-            // Staging for the TMA reduction, 4 KB per warp: column groups 0, 1 use the dS tile (idle until the next chunk's
-            // dS is stored), groups 2, 3 this chunk's dO slot (dV(c) has consumed it; the producer refills it only after
-            // these warps have released it).  The reductions drain while the next chunk is computed.
             {
-                const int g = quad * 2 + (part & 1);
-                const uint32_t region = (part < 2 ? sDS : sRing2 + (uint32_t)(c % kFRing) * kTile) + ((uint32_t)g << 12);
-                const uint32_t mine = region + (uint32_t)lane * 128u;
+                const uint32_t mine = (part < 2 ? sDS : sRing2 + (uint32_t)(c % kFRing) * kTile) + stage_off;
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(mine + ((((uint32_t)j) ^ ((uint32_t)lane & 7u)) << 4)),
@@ -779,16 +804,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                                  : "memory");
                 fence_proxy_async();
                 __syncwarp();
-#ifndef TT_FUSED_NO_RED
-                if (lane == 0) {
-                    tma_reduce_add_2d(&tmDQ, region, part * kCols, bh * p.s_pad + chunk_of(c) * BC + quad * 32);
-                    bulk_commit();
-                }
-#endif
+                if (lane == 0) mbar_arrive(part < 2 ? staged_a : staged_b);
             }
             if (threadIdx.x == 64) TT_STAMP(9);
         }
-        if (lane == 0) bulk_wait_all();
         // ------------------------------------------------------------ epilogue: dV (unscaled), dK (x softmax scale)
         if (!mbar_wait(acc_final, 0, &abort_flag)) goto done;
         tc_fence_after();
@@ -989,7 +1008,7 @@ extern "C" int tt_attn_bwd_fused(const void* q, const void* k, const void* v, co
 #endif
     p.out1 = (__nv_bfloat16*)dv;
     p.out2 = (__nv_bfloat16*)dk;
-    attn_bwd_fused_kernel<<<dim3((S + BS - 1) / BS, (unsigned)BH), kThreads, kFSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, tdq, p);
+    attn_bwd_fused_kernel<<<dim3((S + BS - 1) / BS, (unsigned)BH), kFThreads, kFSmemBytes, st>>>(tq_s, tk_s, tv_s, tdo_s, tdq, p);
     TT_CHECK_LAUNCH();
     const long n8 = (long)BH * S * (D / 8);
     long blocks = (n8 + 255) / 256;
