@@ -73,8 +73,10 @@ struct BwdParams {
 
 #ifdef TT_ATTN_STAMPS
 #define TT_STAMP(slot) do { if (p.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && c < 256) p.stamps[c * 10 + (slot)] = clock64(); } while (0)
+#define TT_STAMPF(slot) do { if (p.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && c < 256) p.stamps[c * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TT_STAMP(slot) do { } while (0)
+#define TT_STAMPF(slot) do { } while (0)
 #endif
 
 // delta[bh, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (token, head)
@@ -580,10 +582,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const int s = c % kFRing;
                 const uint32_t wpar = ((uint32_t)(c / kFRing) & 1u) ^ 1u;
                 if (!mbar_wait(b1_empty(s), wpar, &abort_flag)) goto done;
+                TT_STAMPF(15);
                 mbar_arrive_expect_tx(b1_full(s), kTile);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) tma_load_3d(sRing1 + s * kTile + h * kSlab, &tmQ, b1_full(s), h * 64, chunk_of(c) * BC, bh);
                 if (!mbar_wait(b2_empty(s), wpar, &abort_flag)) goto done;
+                TT_STAMPF(14);
                 mbar_arrive_expect_tx(b2_full(s), kTile);
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
@@ -624,9 +628,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const bool more = c + 1 < n_chunks;
                 const int slot = c % kFRing, nslot = (c + 1) % kFRing;
                 const uint32_t npar = (uint32_t)((c + 1) / kFRing) & 1u;
-                TT_STAMP(0);
+                TT_STAMPF(0);
                 if (!mbar_wait(p_ready, par, &abort_flag)) goto done;              // S(c) has been read: T1 is free
-                TT_STAMP(1);
+                TT_STAMPF(1);
                 tc_fence_after();
                 if (more) {
                     if (!mbar_wait(b1_full(nslot), npar, &abort_flag)) goto done;
@@ -635,7 +639,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_commit(s_full);
                 }
                 if (!mbar_wait(ds_ready, par, &abort_flag)) goto done;             // P, dS in T2; dS in shared memory
-                TT_STAMP(2);
+                TT_STAMPF(2);
                 tc_fence_after();
                 issue_acc(kAccK, kT2 + 16, sRing1 + slot * kTile, c == 0);          // dK += dS^T Q
                 umma_commit(b1_empty(slot));
@@ -646,11 +650,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     umma_bf16_ss(tmem + kT2, smem_desc_sw128(sDS + kk * 2048, kSlab, 1024),
                                  smem_desc_sw128(sA1 + kk * 2048, kSlab, 1024), idesc_q, kk ? 1u : 0u);
                 umma_commit(dq_full);
-                TT_STAMP(3);
+                TT_STAMPF(3);
                 if (more) {
                     if (!mbar_wait(dq_read, par, &abort_flag)) goto done;          // dQ(c) is in registers: T2 is free
-                    TT_STAMP(4);
+                    TT_STAMPF(4);
                     if (!mbar_wait(b2_full(nslot), npar, &abort_flag)) goto done;
+                    TT_STAMPF(10);
                     tc_fence_after();
                     issue_t(kT2, sA2, sRing2 + nslot * kTile);                     // dP(c+1)
                     umma_commit(dp_full);
@@ -670,6 +675,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const uint32_t par = (uint32_t)c & 1u;
                 const int yrow = bh * p.s_pad + chunk_of(c) * BC;
                 if (!mbar_wait(staged_a, par, &abort_flag)) goto done;
+                TT_STAMPF(11);
 #ifndef TT_FUSED_NO_RED
 #pragma unroll
                 for (int g = 0; g < 8; ++g) tma_reduce_add_2d(&tmDQ, sDS + ((uint32_t)g << 12), (g & 1) * kCols, yrow + (g >> 1) * 32);
@@ -684,8 +690,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #endif
                 bulk_commit();
                 bulk_wait_read_but_last();
+                TT_STAMPF(12);
                 mbar_arrive(stage_done);
                 bulk_wait_read();
+                TT_STAMPF(13);
                 mbar_arrive(b2_empty(c % kFRing));
             }
             bulk_wait_all();
@@ -744,7 +752,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const float4* del4 = reinterpret_cast<const float4*>(p.delta + (long)bh * p.pitch + col0);
             // ---- dS(c) from dP(c) and the P kept in registers
             if (!mbar_wait(dp_full, par, &abort_flag)) goto done;
-            if (threadIdx.x == 64) TT_STAMP(5);
+            if (threadIdx.x == 64) TT_STAMPF(5);
             tc_fence_after();
             uint32_t dk[16];
             {
@@ -781,13 +789,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_ready);
-            if (threadIdx.x == 64) TT_STAMP(6);
+            if (threadIdx.x == 64) TT_STAMPF(6);
             // ---- P(c+1): runs while the tensor core forms dK(c), dV(c), dQ(c)
             if (c + 1 < n_chunks && !p_pass(c + 1)) goto done;
-            if (threadIdx.x == 64) TT_STAMP(7);
+            if (threadIdx.x == 64) TT_STAMPF(7);
             // ---- dQ(c) out of T2 and into the global accumulator
             if (!mbar_wait(dq_full, par, &abort_flag)) goto done;
-            if (threadIdx.x == 64) TT_STAMP(8);
+            if (threadIdx.x == 64) TT_STAMPF(8);
             tc_fence_after();
             uint32_t r[32];
             tmem_ld_32x32(t2, r);
@@ -806,7 +814,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(part < 2 ? staged_a : staged_b);
             }
-            if (threadIdx.x == 64) TT_STAMP(9);
+            if (threadIdx.x == 64) TT_STAMPF(9);
         }
         // ------------------------------------------------------------ epilogue: dV (unscaled), dK (x softmax scale)
         if (!mbar_wait(acc_final, 0, &abort_flag)) goto done;
