@@ -53,6 +53,8 @@ def parse():
     p.add_argument("--seq-pad-multiple", type=int, default=8,
                    help="pad each context-parallel chunk to a multiple of this many tokens (8 keeps the weight-gradient GEMMs of "
                         "cp4 / cp8 runs on the tcgen05 kernel; the pad keys are masked)")
+    p.add_argument("--op-profile", type=str, default=None,
+                   help="after the timed loop, run one step under torch.profiler and write the eager-op table to this file")
     p.add_argument("--breakdown", type=str, default=None,
                    help="after the timed loops, run one more step with per-kernel-family device timing (CUDA events around "
                         "every native call and NCCL section) and write the table to this file")
@@ -128,6 +130,20 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_op_profile(step_fn, path, rank):
+    """One more step under torch.profiler: the PyTorch eager ops (cat, add, sum, fill, copies) that remain between the
+    native kernels, grouped by input shape and sorted by device time.  A diagnosis aid; nothing timed here is reported."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True) as prof:
+        step_fn()
+        torch.cuda.synchronize()
+    if rank == 0:
+        with open(path, "w") as fh:
+            fh.write(prof.key_averages(group_by_input_shape=True).table(sort_by="cuda_time_total", row_limit=70,
+                                                                       max_name_column_width=60, max_shapes_column_width=100))
 
 
 def run_breakdown(step_fn, dev):
@@ -344,6 +360,8 @@ def main():
                                             cfg.attention_head_dim, cfg.num_layers + cfg.num_single_layers, rec,
                                             attention_recomputed=not cfg.recompute_save_attention)
     flops, flops_executed = fl(False), fl(not a.no_recompute)
+    if a.op_profile:
+        run_op_profile(lambda: train_step(fwd_device, None, model, optimizer, scheduler, args), a.op_profile, rank)
     breakdown = None
     if a.breakdown:
         breakdown = run_breakdown(lambda: train_step(fwd_device, None, model, optimizer, scheduler, args), dev)

@@ -126,6 +126,15 @@ class RowParallelLinear(nn.Module):
         y = tp_region_output(y, self.sequence_parallel, row_splits)
         return y if self.bias is None else y + self.bias
 
+    def forward_merged(self, x1: torch.Tensor, x2: torch.Tensor, row_splits: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """Same for an input given as its two feature groups (``input_partitions``): ``cat([x1, x2], -1)`` is projected,
+        and the backward keeps the two gradients apart (:func:`teletron_b200.ops.linear_merged`)."""
+        if self.tp == 1:
+            return ops.linear_merged(x1, x2, self.weight, self.bias)
+        y = ops.linear_merged(x1, x2, self.weight, None)
+        y = tp_region_output(y, self.sequence_parallel, row_splits)
+        return y if self.bias is None else y + self.bias
+
 
 
 class RMSNorm(nn.Module):
@@ -497,8 +506,7 @@ class HunyuanSingleDiTLayer(nn.Module):
             proj = self._attention_and_projection_fused(hn, mlp, T, cos, sin, pad, kv_valid_len, in_region=sp)
         else:
             attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len, in_region=sp)
-            merged = torch.cat([torch.cat([attn, c_attn], dim=1), mlp], dim=2)
-            proj = self.proj_out(merged, row_splits=splits)
+            proj = self.proj_out.forward_merged(torch.cat([attn, c_attn], dim=1), mlp, row_splits=splits)
         h = ops.gate_residual(h, proj, gate)
         return h[:, :-T_own], h[:, -T_own:]
 

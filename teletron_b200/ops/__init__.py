@@ -131,6 +131,14 @@ def linear(x, weight, bias=None, activation=None):
     return reference.linear(x, weight, bias, activation)
 
 
+def linear_merged(x1, x2, weight, bias=None):
+    """``cat([x1, x2], -1) @ weight^T + bias`` without ever forming the concatenated gradient in the backward."""
+    if _use_cuda(x1):
+        from . import cuda_ops
+        return cuda_ops.linear_merged(x1, x2, weight, bias)
+    return reference.linear_merged(x1, x2, weight, bias)
+
+
 def attention(q, k, v, kv_valid_len=None, scale=None, mask_range=None):
     """``kv_valid_len`` masks the key tail, ``mask_range = (lo, hi)`` one more key range."""
     if _use_cuda(q):

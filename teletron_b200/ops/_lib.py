@@ -76,7 +76,16 @@ def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_CUR_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device as a raw handle.  Every native call asks for it, so it goes
+    through the two C entry points directly: ``torch.cuda.current_stream()`` resolves its device argument through
+    ``device_count()``, which was measured at ~45 us per call (0.7 s over 15 700 native calls of six training steps)."""
+    if _RAW_STREAM is not None and _CUR_DEVICE is not None:
+        return ctypes.c_void_p(_RAW_STREAM(_CUR_DEVICE()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

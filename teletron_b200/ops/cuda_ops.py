@@ -243,6 +243,46 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db, None
 
 
+class _LinearMerged(torch.autograd.Function):
+    """``y = cat([x1, x2], -1) @ weight^T + bias`` for the single-stream block's merged projection (attention output and
+    MLP activation side by side).  The forward concatenates once and runs one GEMM; the backward never forms the
+    concatenated gradient: each input's gradient comes from its own GEMM against a column slice of the weight (a strided
+    B operand), and each half of the weight gradient is written into its column slice of ``dW``, so no strided slice
+    of a ``[tokens, k1 + k2]`` gradient has to be copied to make it contiguous."""
+
+    @staticmethod
+    def forward(ctx, x1, x2, weight, bias):
+        k1, k2 = x1.shape[-1], x2.shape[-1]
+        a1, a2 = x1.reshape(-1, k1), x2.reshape(-1, k2)
+        y = _gemm_nt(torch.cat([a1, a2], dim=1), weight, bias)
+        ctx.save_for_backward(a1, a2, weight)
+        ctx.has_bias = bias is not None
+        ctx.lead = x1.shape[:-1]
+        return y.view(*x1.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import gemm
+        a1, a2, weight = ctx.saved_tensors
+        k1 = a1.shape[1]
+        du = dy.reshape(-1, weight.shape[0])
+        if not du.is_contiguous():
+            du = du.contiguous()
+        d1 = _gemm_nn(du, weight[:, :k1]).view(*ctx.lead, k1) if ctx.needs_input_grad[0] else None
+        d2 = _gemm_nn(du, weight[:, k1:]).view(*ctx.lead, a2.shape[1]) if ctx.needs_input_grad[1] else None
+        dw = None
+        if ctx.needs_input_grad[2]:
+            dw = torch.empty_like(weight)
+            gemm.gemm_tn_into(du, a1, dw[:, :k1])
+            gemm.gemm_tn_into(du, a2, dw[:, k1:])
+        db = du.sum(dim=0, dtype=torch.float32).to(du.dtype) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+        return d1, d2, dw, db
+
+
+def linear_merged(x1, x2, weight, bias=None):
+    return _LinearMerged.apply(x1, x2, weight, bias)
+
+
 def linear(x, weight, bias=None, activation=None):
     if activation not in (None, "gelu", "gelu_tanh"):
         from . import reference

@@ -86,6 +86,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return _act(F.linear(x, weight, bias), activation)
 
 
+def linear_merged(x1: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``cat([x1, x2], -1) @ weight.T + bias``: the single-stream block's projection of ``[attention | MLP]``."""
+    return F.linear(torch.cat([x1, x2], dim=-1), weight, bias)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               kv_valid_len: Optional[int] = None, scale: Optional[float] = None, mask_range=None) -> torch.Tensor:
     """Non-causal softmax attention.

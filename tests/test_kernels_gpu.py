@@ -148,6 +148,28 @@ def test_linear(act):
         assert _rel(a, r) < 1.5e-2
 
 
+def test_linear_merged_keeps_the_two_gradients_apart():
+    """Projection of ``[x1 | x2]``: value and all four gradients against fp32; both halves of dW come from GEMMs that
+    write column slices of one matrix, both input gradients from GEMMs that read column slices of the weight."""
+    from teletron_b200.ops import cuda_ops, gemm, reference
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x1 = torch.randn(1, 2104, 384, device=_dev(), generator=g).bfloat16().requires_grad_()
+    x2 = torch.randn(1, 2104, 1536, device=_dev(), generator=g).bfloat16().requires_grad_()
+    w = (torch.randn(768, 1920, device=_dev(), generator=g) * 0.05).bfloat16().requires_grad_()
+    b = torch.randn(768, device=_dev(), generator=g).bfloat16().requires_grad_()
+    d = torch.randn(1, 2104, 768, device=_dev(), generator=g).bfloat16()
+    before = (gemm.COUNTERS["tcgen05"], gemm.COUNTERS["cublas"])
+    y = cuda_ops.linear_merged(x1, x2, w, b)
+    y.backward(d)
+    assert gemm.COUNTERS["tcgen05"] - before[0] == 5 and gemm.COUNTERS["cublas"] == before[1]
+    refs = [t.detach().float().requires_grad_() for t in (x1, x2, w, b)]
+    yr = reference.linear_merged(*refs)
+    yr.backward(d.float())
+    assert _rel(y, yr) < 1e-2
+    for a, r in zip((x1.grad, x2.grad, w.grad, b.grad), (t.grad for t in refs)):
+        assert _rel(a, r) < 1.5e-2
+
+
 @pytest.mark.parametrize("mode,state", [("fp32", torch.float32), ("split16", torch.bfloat16), ("none", torch.float32),
                                         ("split16", torch.float32)])
 def test_adamw(mode, state):
