@@ -209,7 +209,7 @@ def _joint_attention(q, k, v, text_len: int, kv_valid_len: Optional[int]):
     """Single-rank case: q, k, v already hold ``cat(video, text)`` as ``[B, h, S + T, D]``."""
     S = q.shape[2] - text_len
     o = ops.attention(q, k, v, kv_valid_len=None if kv_valid_len is None else S + kv_valid_len)
-    return o[:, :S], o[:, S:]
+    return M.split_tokens(o, S)
 
 
 def _ulysses_attention(q, k, v, tq, tk, tv, pad: Optional[SeqPad], kv_valid_len: Optional[int]):
@@ -508,7 +508,7 @@ class HunyuanSingleDiTLayer(nn.Module):
             attn, c_attn = self.self_attention(hn, T, cos, sin, pad, kv_valid_len, in_region=sp)
             proj = self.proj_out.forward_merged(torch.cat([attn, c_attn], dim=1), mlp, row_splits=splits)
         h = ops.gate_residual(h, proj, gate)
-        return h[:, :-T_own], h[:, -T_own:]
+        return M.split_tokens(h, h.shape[1] - T_own)
 
     def _attention_and_projection_fused(self, hn, mlp, T, cos, sin, pad, kv_valid_len, in_region: bool = False):
         """Single-stream block with both Ulysses all-to-alls fused: the QKV epilogue scatters heads to their owners and

@@ -332,3 +332,25 @@ def gather_from_tensor_model_parallel_region_reduce_grad(x, group):
     if _size(group) == 1:
         return x
     return _GatherFromTPReduceGrad.apply(x, group)
+
+
+class _SplitTokens(torch.autograd.Function):
+    """``x[:, :n], x[:, n:]`` whose backward is one concatenation.  Two plain slices would each get a zero-filled
+    full-size gradient with the slice copied in, and the two would then be added: three passes over the whole tensor
+    where one copy suffices (measured at 450 us against 65 us per split of a [1, 32656, 3072] bf16 tensor)."""
+
+    @staticmethod
+    def forward(ctx, x, n):
+        ctx.n = n
+        return x[:, :n], x[:, n:]
+
+    @staticmethod
+    def backward(ctx, da, db):
+        return torch.cat([da, db], dim=1), None
+
+
+def split_tokens(x: torch.Tensor, n: int):
+    """Split ``[B, N, ...]`` after ``n`` tokens (views of ``x``; do not modify them in place)."""
+    if not x.requires_grad or not torch.is_grad_enabled():
+        return x[:, :n], x[:, n:]
+    return _SplitTokens.apply(x, n)
