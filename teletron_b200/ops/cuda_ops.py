@@ -7,6 +7,7 @@ column reductions are allocated here with ``torch.empty`` and handed to the C si
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -16,6 +17,8 @@ from ._lib import c_float, c_int, c_long, call, check, ptr, stream
 
 BF16 = torch.bfloat16
 _GELU_KIND = {"gelu": 0, "gelu_tanh": 1}
+# TELETRON_B200_GELU_EPILOGUE=0 keeps the activation in its own kernel after the GEMM
+_FUSE_GELU_EPILOGUE = os.environ.get("TELETRON_B200_GELU_EPILOGUE", "1") != "0"
 
 
 def _rows_cols(x: torch.Tensor):
@@ -212,9 +215,18 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, weight, bias, activation):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
-        u = _gemm_nt(x2, weight, bias)
         ctx.activation = activation
         ctx.has_bias = bias is not None
+        if activation is not None and _FUSE_GELU_EPILOGUE:
+            # bias + GELU in the GEMM epilogue: the accumulator is activated in fp32 and the kernel writes both the
+            # activated output and the bf16 pre-activation that the backward needs
+            from . import gemm, gemm_tcgen05
+            if gemm.get_backend() != "cublas" and gemm_tcgen05.supported(x2, weight, "nt"):
+                gemm.COUNTERS["tcgen05"] += 1
+                y, u = gemm_tcgen05.gemm(x2, weight, "nt", bias, epi=1 + _GELU_KIND[activation])
+                ctx.save_for_backward(x2, weight, u)
+                return y.view(*x.shape[:-1], weight.shape[0])
+        u = _gemm_nt(x2, weight, bias)
         if activation is None:
             ctx.save_for_backward(x2, weight)
             return u.view(*x.shape[:-1], weight.shape[0])
