@@ -446,3 +446,38 @@ def test_restart_wrapper_relaunches_only_on_watchdog_exit(tmp_path):
     # the restart budget is respected
     r = subprocess.run(["bash", script, "bash", "-c", "exit 75"], env=dict(env, MAX_RESTARTS="1"), capture_output=True, text=True)
     assert r.returncode == 75 and "giving up" in r.stderr
+
+
+def test_split_tokens_backward_is_one_concatenation():
+    """``split_tokens`` returns the two slices; its gradient equals that of plain slicing, also when one half is unused."""
+    from teletron_b200.parallel.mappings import split_tokens
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 9, 5, generator=g, requires_grad=True)
+    y = x.detach().clone().requires_grad_()
+    a, b = split_tokens(x * 1.0, 6)
+    ra, rb = (y * 1.0)[:, :6], (y * 1.0)[:, 6:]
+    assert a.shape == (2, 6, 5) and b.shape == (2, 3, 5) and torch.equal(a, ra) and torch.equal(b, rb)
+    wa, wb = torch.randn(2, 6, 5, generator=g), torch.randn(2, 3, 5, generator=g)
+    ((a * wa).sum() + (b * wb).sum()).backward()
+    ((ra * wa).sum() + (rb * wb).sum()).backward()
+    torch.testing.assert_close(x.grad, y.grad)
+    x.grad = None
+    a, _ = split_tokens(x * 1.0, 6)
+    (a * wa).sum().backward()
+    assert float(x.grad[:, 6:].abs().max()) == 0.0 and torch.allclose(x.grad[:, :6], wa)
+    # without autograd it is plain slicing
+    with torch.no_grad():
+        p, q = split_tokens(x, 4)
+    assert p.shape[1] == 4 and q.shape[1] == 5
+
+
+def test_linear_merged_matches_linear_of_the_concatenation():
+    from teletron_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    x1, x2 = torch.randn(1, 7, 6, generator=g, requires_grad=True), torch.randn(1, 7, 10, generator=g, requires_grad=True)
+    w, b = torch.randn(4, 16, generator=g, requires_grad=True), torch.randn(4, generator=g, requires_grad=True)
+    y = ops.linear_merged(x1, x2, w, b)
+    ref = torch.nn.functional.linear(torch.cat([x1, x2], -1), w, b)
+    torch.testing.assert_close(y, ref)
+    y.square().sum().backward()
+    assert x1.grad.shape == x1.shape and x2.grad.shape == x2.shape and w.grad.shape == w.shape
