@@ -1,5 +1,7 @@
-// Flash attention backward on tcgen05 / TMEM (head dim 128, non-causal, key-length mask), split into two
-// atomics-free, deterministic kernels built from one template:
+// Flash attention backward on tcgen05 / TMEM (head dim 128, non-causal, key-length mask).  Two variants share this file:
+// the one-pass kernel further down (attn_bwd_fused_kernel: five products per tile pair, dQ reduced in fp32 by the TMA
+// unit; what the Python layer calls by default) and, described first, the split into two atomics-free, deterministic
+// kernels built from one template (seven products per tile pair):
 //
 //   KV-stationary (dK, dV): a CTA owns 128 keys (K, V tiles resident in shared memory) and streams the
 //     queries in chunks of 128 rows (Q, dO).   T1 = K Q^T = S^T,  T2 = V dO^T = dP^T,
