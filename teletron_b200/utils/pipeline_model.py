@@ -24,7 +24,7 @@ The programs below are transcribed from the kernel; a change of the kernel's syn
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, FrozenSet, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 RING = 2            # slots of the streamed Q and dO rings
 
