@@ -8,8 +8,8 @@ tensors; frames are temporally sampled by fragment samplers (``:416-547``), spat
 grid "fragments" (``:122-226``), normalised with ImageNet mean / std and returned as
 ``images [F, 3, H, W]`` plus the text / latent fields.
 
-Decoding uses ``decord`` when it is installed; otherwise clips stored as ``.pt`` / ``.npy`` uint8 arrays
-``[T, H, W, 3]`` are read, which is also what the unit tests use.  The reference's quirks are not kept:
+Decoding uses ``decord`` when it is installed, else OpenCV; clips may also be stored as ``.pt`` / ``.npy`` uint8 arrays
+``[T, H, W, 3]``, which is what most unit tests use.  The reference's quirks are not kept:
 length is the number of annotation entries times ``repeat`` (the reference indexes ``% 9`` with a
 fixed length of 100000, ``:682, 706-707``).
 """
@@ -264,22 +264,75 @@ def get_spatial_samples(video: torch.Tensor, random_crop: int = 0, sample_types:
     return {name: get_single_sample(video, name, **(opt or {})) for name, opt in sample_types.items()}
 
 
+def _decord():
+    try:
+        import decord  # type: ignore
+        return decord
+    except ImportError:
+        return None
+
+
+def _cv2_read(path: str, frame_indices: Optional[np.ndarray]) -> torch.Tensor:
+    """Decode with OpenCV: the requested frames in one forward pass over the file (seeking per frame is slow and, with
+    some codecs, inexact)."""
+    import cv2
+    cap = cv2.VideoCapture(path)
+    if not cap.isOpened():
+        raise RuntimeError(f"cannot open {path}")
+    try:
+        total = int(cap.get(cv2.CAP_PROP_FRAME_COUNT))
+        frames = []
+        if frame_indices is None:
+            while True:
+                ok, f = cap.read()
+                if not ok:
+                    break
+                frames.append(f[:, :, ::-1])
+            return torch.from_numpy(np.ascontiguousarray(np.stack(frames)))
+        if total <= 0:
+            raise RuntimeError(f"{path}: the container does not report a frame count")
+        want = np.mod(np.asarray(frame_indices), total)
+        last, pos, cache = int(want.max()), 0, {}
+        needed = set(int(i) for i in want)
+        while pos <= last:
+            ok, f = cap.read()
+            if not ok:
+                break
+            if pos in needed:
+                cache[pos] = f[:, :, ::-1]
+            pos += 1
+        if len(cache) < len(needed):       # a container that reports more frames than it holds: repeat the last one
+            tail = cache[max(cache)] if cache else None
+            if tail is None:
+                raise RuntimeError(f"{path}: no frame could be decoded")
+            for i in needed - set(cache):
+                cache[i] = tail
+        return torch.from_numpy(np.ascontiguousarray(np.stack([cache[int(i)] for i in want])))
+    finally:
+        cap.release()
+
+
 def read_video(path: str, frame_indices: Optional[np.ndarray] = None) -> torch.Tensor:
-    """``[T, H, W, 3]`` uint8 frames (all, or the requested indices)."""
+    """``[T, H, W, 3]`` uint8 RGB frames (all, or the requested indices).  ``.pt`` / ``.npy`` hold the array itself;
+    container files (``.mp4``, ``.avi``, ...) are decoded with ``decord`` as the reference does
+    (``koala_dataset.py``), or with OpenCV when ``decord`` is not installed."""
     ext = os.path.splitext(path)[1].lower()
     if ext == ".pt":
         v = torch.load(path)
     elif ext == ".npy":
         v = torch.from_numpy(np.load(path))
     else:
+        decord = _decord()
+        if decord is not None:
+            vr = decord.VideoReader(path)
+            idx = list(range(len(vr))) if frame_indices is None else np.mod(frame_indices, len(vr)).tolist()
+            return torch.from_numpy(vr.get_batch(idx).asnumpy())
         try:
-            import decord  # type: ignore
+            import cv2  # noqa: F401
         except ImportError as e:
-            raise RuntimeError(f"decoding {path} needs the `decord` package, which is not installed; "
-                               "store clips as .pt / .npy uint8 [T,H,W,3] or install decord") from e
-        vr = decord.VideoReader(path)
-        idx = list(range(len(vr))) if frame_indices is None else np.mod(frame_indices, len(vr)).tolist()
-        return torch.from_numpy(vr.get_batch(idx).asnumpy())
+            raise RuntimeError(f"decoding {path} needs `decord` or OpenCV, neither is installed; "
+                               "store clips as .pt / .npy uint8 [T,H,W,3]") from e
+        return _cv2_read(path, frame_indices)
     if frame_indices is not None:
         v = v[torch.from_numpy(np.mod(frame_indices, v.shape[0]))]
     return v
@@ -289,8 +342,18 @@ def video_num_frames(path: str) -> int:
     ext = os.path.splitext(path)[1].lower()
     if ext in (".pt", ".npy"):
         return int(read_video(path).shape[0])
-    import decord  # type: ignore
-    return len(decord.VideoReader(path))
+    decord = _decord()
+    if decord is not None:
+        return len(decord.VideoReader(path))
+    import cv2
+    cap = cv2.VideoCapture(path)
+    try:
+        n = int(cap.get(cv2.CAP_PROP_FRAME_COUNT)) if cap.isOpened() else 0
+    finally:
+        cap.release()
+    if n <= 0:
+        raise RuntimeError(f"cannot read the frame count of {path}")
+    return n
 
 
 def get_spatial_and_temporal_samples(path: str, sample_types: Dict[str, dict], samplers: Dict[str, object],

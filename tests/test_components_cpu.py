@@ -481,3 +481,27 @@ def test_linear_merged_matches_linear_of_the_concatenation():
     torch.testing.assert_close(y, ref)
     y.square().sum().backward()
     assert x1.grad.shape == x1.shape and x2.grad.shape == x2.shape and w.grad.shape == w.shape
+
+
+def test_read_video_decodes_a_container_file_with_opencv(tmp_path):
+    """Without ``decord`` the dataset decodes ``.mp4`` / ``.avi`` clips through OpenCV: frame count, requested indices
+    (wrapping past the end) and RGB channel order."""
+    cv2 = pytest.importorskip("cv2")
+    import numpy as np
+    from teletron_b200.data.koala_dataset import read_video, video_num_frames
+    path = str(tmp_path / "clip.avi")
+    w = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"MJPG"), 10.0, (64, 48))
+    if not w.isOpened():
+        pytest.skip("this OpenCV build cannot write MJPG")
+    for i in range(6):
+        frame = np.zeros((48, 64, 3), dtype=np.uint8)
+        frame[..., 2] = 40 * i + 20            # OpenCV frames are BGR: this is the red channel
+        w.write(frame)
+    w.release()
+    assert video_num_frames(path) == 6
+    v = read_video(path)
+    assert v.shape == (6, 48, 64, 3) and v.dtype == torch.uint8
+    red = v[..., 0].float().mean(dim=(1, 2))
+    assert torch.all(red[1:] > red[:-1]) and float(v[..., 2].float().mean()) < 12        # red grows, blue stays dark
+    sel = read_video(path, np.array([4, 1, 7]))                                           # 7 wraps to 1
+    assert sel.shape[0] == 3 and torch.equal(sel[1], sel[2]) and torch.equal(sel[0], v[4])
